@@ -1,0 +1,86 @@
+"""ctypes loader for libfastbb_b200.so, the C-ABI shared library holding the sm_100a kernels.
+
+Plays the role of the reference's driver-API loader (fastbb/kernels.py:71-133 `Kernels`): the host code stays
+Python/PyTorch and crosses one thin FFI boundary per operator. Differences: the boundary is a C ABI with one
+entry point per operator instead of a kernel-name + signature-string table; a non-zero status becomes a Python
+exception; nothing is cached per device in Python, so several GPUs can be used from one process.
+There is no CPU or PyTorch fallback: if the library is missing, importing an operator raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfastbb_b200.so")
+
+FBB_OK = 0
+DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+EPI_NONE, EPI_GELU, EPI_SWIGLU = 0, 1, 2
+ACC_F32, ACC_F16 = 0, 1
+FLASH_VARIANT = {"ff": 0, "fh": 1, "hh": 2}
+
+_vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/fastbb_b200.h one to one.
+PROTOTYPES = {
+    "fbb_version": (_i32, []),
+    "fbb_status_string": (ctypes.c_char_p, [_i32]),
+    "fbb_last_error": (ctypes.c_char_p, []),
+    "fbb_device_status": (_i32, [ctypes.POINTER(ctypes.c_uint * 4)]),
+    "fbb_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _f32, _i32, _i32, _vp]),
+    "fbb_linear_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
+}
+
+
+class FastbbError(RuntimeError):
+    """A non-zero status from libfastbb_b200.so (negative: rejected arguments; positive: a CUDA error code)."""
+
+    def __init__(self, status, message):
+        super().__init__(f"fastbb_b200 status {status}: {message}")
+        self.status = status
+
+
+_LIB = None
+
+
+def load(path=None):
+    """Load (once) and return the ctypes handle with every prototype set. Raises OSError if the library is not built."""
+    global _LIB
+    if _LIB is None or path is not None:
+        p = path or LIB_PATH
+        if not os.path.exists(p):
+            raise OSError(f"{p} not found: build it with `python -m fastbb_b200.build` (needs nvcc with sm_100a support); "
+                          "there is no fallback path")
+        lib = ctypes.CDLL(p)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        if path is not None:
+            return lib
+        _LIB = lib
+    return _LIB
+
+
+def check(status):
+    if status != FBB_OK:
+        lib = load()
+        msg = lib.fbb_last_error().decode() or lib.fbb_status_string(status).decode()
+        raise FastbbError(status, msg)
+
+
+def stream_ptr(device=None):
+    """cudaStream_t of torch's current stream on `device` as an integer (0 = legacy default stream)."""
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def device_status():
+    """Synchronise the current device and raise FastbbError if any kernel gave up a bounded wait."""
+    out = (ctypes.c_uint * 4)()
+    check(load().fbb_device_status(ctypes.byref(out)))
+    return tuple(out)

@@ -1,0 +1,157 @@
+// The extern "C" surface of libfastbb_b200.so: argument validation on the host, then one launch per call.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace fbb {
+
+static thread_local char t_last_error[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+        if (q != cudaDriverEntryPointSuccess) return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
+                  const uint32_t* box) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[4];
+    cuuint32_t bx[5];
+    cuuint32_t es[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i > 0) gstr[i - 1] = (cuuint64_t)strides_elems[i] * 2u;
+    }
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FBB_OK;
+}
+
+int num_sms() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace fbb
+
+using namespace fbb;
+
+extern "C" {
+
+int fbb_version(void) { return FBB_VERSION; }
+
+const char* fbb_status_string(int status) {
+    switch (status) {
+        case FBB_OK: return "ok";
+        case FBB_ERR_NULL: return "a required pointer is null";
+        case FBB_ERR_SHAPE: return "unsupported size or leading dimension";
+        case FBB_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
+        case FBB_ERR_ENUM: return "unknown enum value";
+        case FBB_ERR_DRIVER: return "CUDA driver tensor-map entry point failed";
+        case FBB_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+const char* fbb_last_error(void) { return t_last_error; }
+
+int fbb_device_status(unsigned int out[4]) {
+    if (out == nullptr) return fail(FBB_ERR_NULL, "fbb_device_status: out is null");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail((int)e, "fbb_device_status: %s", cudaGetErrorString(e));
+    e = cudaMemcpyFromSymbol(out, g_fbb_status, sizeof(unsigned int) * 4);
+    if (e != cudaSuccess) return fail((int)e, "fbb_device_status: %s", cudaGetErrorString(e));
+    if (out[0] != 0u || out[3] != 0u) {
+        const unsigned int zero[4] = {0u, 0u, 0u, 0u};
+        cudaMemcpyToSymbol(g_fbb_status, zero, sizeof(zero));
+        return fail(FBB_ERR_DEVICE_WAIT, "device wait ran out: code %u detail %u block %u (%u reports)", out[0], out[1],
+                    out[2], out[3]);
+    }
+    return FBB_OK;
+}
+
+int fbb_layernorm_f16(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
+                      float eps, int in_dtype, int param_dtype, void* stream) {
+    if (x == nullptr || y == nullptr) return fail(FBB_ERR_NULL, "layernorm: x or y is null");
+    if (in_dtype < FBB_DTYPE_F16 || in_dtype > FBB_DTYPE_F32 || param_dtype < FBB_DTYPE_F16 || param_dtype > FBB_DTYPE_F32)
+        return fail(FBB_ERR_ENUM, "layernorm: unknown dtype code (in %d, param %d)", in_dtype, param_dtype);
+    if (M < 0 || C <= 0 || (C & 7) != 0) return fail(FBB_ERR_SHAPE, "layernorm: need M >= 0 and C %% 8 == 0 (M=%lld C=%d)", (long long)M, C);
+    if (ldx < C || ldy < C) return fail(FBB_ERR_SHAPE, "layernorm: row stride smaller than C");
+    const int in_vec = in_dtype == FBB_DTYPE_F32 ? 4 : 8;
+    if ((ldx % in_vec) != 0 || (ldy & 7) != 0 || !aligned16(x) || !aligned16(y) || !aligned16(w) || !aligned16(b))
+        return fail(FBB_ERR_ALIGN, "layernorm: pointers must be 16-byte aligned and row strides multiples of 16 bytes");
+    if (!(eps >= 0.f)) return fail(FBB_ERR_SHAPE, "layernorm: eps must be >= 0");
+    return launch_layernorm(x, y, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype, (cudaStream_t)stream);
+}
+
+int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
+                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
+                   void* stream) {
+    if (A == nullptr || W == nullptr || C == nullptr) return fail(FBB_ERR_NULL, "linear: A, W or C is null");
+    if (epilogue < FBB_EPI_NONE || epilogue > FBB_EPI_SWIGLU) return fail(FBB_ERR_ENUM, "linear: unknown epilogue %d", epilogue);
+    if (accumulate != FBB_ACC_F32 && accumulate != FBB_ACC_F16) return fail(FBB_ERR_ENUM, "linear: unknown accumulate %d", accumulate);
+    if (M < 0 || M > 0x7FFFFF00ll || N <= 0 || K <= 0) return fail(FBB_ERR_SHAPE, "linear: bad M/N/K (%lld, %d, %d)", (long long)M, N, K);
+    if ((K & 7) != 0 || (N & 7) != 0) return fail(FBB_ERR_SHAPE, "linear: need K %% 8 == 0 and N %% 8 == 0 (N=%d K=%d)", N, K);
+    const bool swiglu = epilogue == FBB_EPI_SWIGLU;
+    if (swiglu && ((N & 15) != 0 || res != nullptr || gamma != nullptr))
+        return fail(FBB_ERR_SHAPE, "linear: SwiGLU needs N %% 16 == 0 and no res / gamma");
+    const int n_out = swiglu ? N / 2 : N;
+    if (lda < K || ldw < K || ldc < n_out || (res != nullptr && ldr < n_out))
+        return fail(FBB_ERR_SHAPE, "linear: a leading dimension is smaller than its row length");
+    if ((lda & 7) || (ldw & 7) || (ldc & 7) || (res != nullptr && (ldr & 7)) || !aligned16(A) || !aligned16(W) || !aligned16(C) ||
+        !aligned16(res))
+        return fail(FBB_ERR_ALIGN, "linear: A, W, C, res must be 16-byte aligned with leading dimensions %% 8 == 0");
+    return launch_linear(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, (cudaStream_t)stream);
+}
+
+int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                    int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                    int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream) {
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(FBB_ERR_NULL, "flash64: q, k, v or o is null");
+    if (variant < FBB_FLASH_FF || variant > FBB_FLASH_HH) return fail(FBB_ERR_ENUM, "flash64: unknown variant %d", variant);
+    if (B < 0 || N < 0 || H <= 0 || (int64_t)B * H > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: bad B/N/H (%d, %d, %d)", B, N, H);
+    if (!(scale > 0.f)) return fail(FBB_ERR_SHAPE, "flash64: scale must be > 0");
+    const int64_t qs[3] = {q_sb, q_sn, q_sh}, ks[3] = {k_sb, k_sn, k_sh}, vs[3] = {v_sb, v_sn, v_sh}, os[3] = {o_sb, o_sn, o_sh};
+    for (int i = 0; i < 3; ++i)
+        if ((qs[i] & 7) || (ks[i] & 7) || (vs[i] & 7) || (os[i] & 7) || qs[i] < 0 || ks[i] < 0 || vs[i] < 0 || os[i] < 0)
+            return fail(FBB_ERR_ALIGN, "flash64: strides must be non-negative multiples of 8 elements");
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(FBB_ERR_ALIGN, "flash64: pointers must be 16-byte aligned");
+    if (q_sn < 64 || k_sn < 64 || v_sn < 64 || o_sn < 64) return fail(FBB_ERR_SHAPE, "flash64: token stride smaller than the head dimension");
+    if (B == 0 || N == 0) return FBB_OK;
+    return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, (cudaStream_t)stream);
+}
+
+}  // extern "C"

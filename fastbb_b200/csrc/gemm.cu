@@ -1,0 +1,324 @@
+// C[M, Nout] = epilogue(A[M, K] . W[N, K]^T): fp16 operands, tcgen05 UMMA with the accumulator in tensor memory.
+// Replaces F.linear + the separate bias / GELU / SwiGLU / LayerScale-residual passes of fastbb/vit.py:114-143 and the
+// gemm_tn_* kernels of fastbb/fastbb_kernels.cu:323-446 (epilogue order bias -> act -> res + gamma*v, :418-427).
+//
+// Persistent kernel, one CTA per SM, 128 x BN output tiles, K consumed in 64-element (128-byte) blocks:
+//   warp 0      TMA producer: A box [64 x 128] and W box [64 x BN] per stage (128-byte swizzle, zero fill outside)
+//   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage into one of two tensor-memory accumulators
+//   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> 16-byte stores
+// The two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// Both operands are K-major, so neither is transposed: nn.Linear's [N, K] weight is exactly the B operand.
+#include "common.cuh"
+#include "internal.h"
+
+namespace fbb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 320;
+constexpr int kEpiThreads = 256;
+
+template <int BN>
+struct GemmSmem {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kParamFloats = 2 * 2 * BN;  // double-buffered bias + gamma
+    static constexpr int kBarOffset = kStages * kStageBytes + kParamFloats * 4;
+    static constexpr int kNumBars = 2 * kStages + 4;
+    static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kBytes + 1024;  // slack to align the tile base to 1024 bytes
+};
+
+struct GemmArgs {
+    __half* C;
+    const __half* bias;
+    const __half* res;
+    const __half* gamma;
+    int M, N, K;       // N = rows of W
+    int n_out;         // output columns (N, or N/2 for SwiGLU)
+    int64_t ldc, ldr;
+    int act;           // 0 none, 1 gelu
+    int acc_f16;       // 1: fp16 accumulator
+    int tiles_m, tiles_n;
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmArgs g) {
+    using S = GemmSmem<BN>;
+    constexpr int kStages = S::kStages;
+    constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - raw);
+    float* s_params = reinterpret_cast<float*>(gen + kStages * S::kStageBytes);
+    const uint32_t bar0 = base + S::kBarOffset;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + S::kBarOffset + S::kNumBars * 8);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(gen + S::kBarOffset + S::kNumBars * 8 + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_kb = (g.K + BK - 1) / BK;
+    const int num_tiles = g.tiles_m * g.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), kEpiThreads / 32);
+        }
+        *s_abort = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_w);
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc<2 * BN>(smem_u32(const_cast<uint32_t*>(s_tmem)));
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / g.tiles_n) * BM;
+                const int nt = tile % g.tiles_n;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
+                    const uint32_t sa = base + s * S::kStageBytes;
+                    const uint32_t sb = sa + S::kABytes;
+                    mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+                    tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, m0);
+                    if (SWIGLU) {
+                        // x1 rows [nt*BN/2, +BN/2) and the matching x2 rows, offset by N/2
+                        tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * (BN / 2));
+                        tma_load_2d(sb + S::kBBytes / 2, &tmap_w, full_bar(s), kb * BK, g.N / 2 + nt * (BN / 2));
+                    } else {
+                        tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * BN);
+                    }
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!ok) __nanosleep(20000);  // let copies already in flight land before the CTA leaves
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_f16(BM, BN, !g.acc_f16, false, false);
+            constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, acc)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, s)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * S::kStageBytes;
+                    const uint64_t adesc = smem_desc(sa, desc_hi);
+                    const uint64_t bdesc = smem_desc(sa + S::kABytes, desc_hi);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar(s));  // stage reusable once these UMMAs have read it
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));  // accumulator complete
+                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (8 warps)
+        const int ew = warp - 2;
+        const int quad = warp & 3;        // tensor-memory lane quadrant this warp may read
+        const int chalf = ew >> 2;        // which half of the output columns
+        const int et = threadIdx.x - 64;  // 0..255
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int m0 = (tile / g.tiles_n) * BM;
+            const int nt = tile % g.tiles_n;
+            const int n0 = nt * kOutCols;  // first output column of the tile
+            // stage bias (W-row indexed) and gamma (output-column indexed) for this tile
+            float* s_bias = s_params + acc * 2 * BN;
+            float* s_gamma = s_bias + BN;
+            for (int i = et; i < BN; i += kEpiThreads) {
+                int wrow;
+                if (SWIGLU) wrow = i < BN / 2 ? n0 + i : g.N / 2 + n0 + (i - BN / 2);
+                else wrow = n0 + i;
+                const bool in = SWIGLU ? (n0 + (i % (BN / 2)) < g.n_out) : (wrow < g.N);
+                s_bias[i] = (g.bias != nullptr && in) ? __half2float(g.bias[wrow]) : 0.f;
+                if (!SWIGLU) s_gamma[i] = (g.gamma != nullptr && in) ? __half2float(g.gamma[wrow]) : 1.f;
+            }
+            named_bar_sync(1, kEpiThreads);
+            if (!mbar_wait(tfull_bar(acc), acc_ph, s_abort, DEV_TIMEOUT_TMEM_FULL, acc)) break;
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+            const bool row_ok = row < g.M;
+            __half* c_row = g.C + (int64_t)row * g.ldc;
+            const __half* r_row = g.res != nullptr ? g.res + (int64_t)row * g.ldr : nullptr;
+#pragma unroll 1
+            for (int c0 = chalf * (kOutCols / 2); c0 < (chalf + 1) * (kOutCols / 2); c0 += 32) {
+                uint32_t r[32];
+                float v[32];
+                tmem_ld32(t_row + (uint32_t)c0, r);
+                tmem_wait_ld();
+                if (g.acc_f16) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __half2float(__ushort_as_half((unsigned short)(r[j] & 0xFFFFu)));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                }
+                if (SWIGLU) {
+                    uint32_t r2[32];
+                    tmem_ld32(t_row + (uint32_t)(BN / 2 + c0), r2);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x2 = (g.acc_f16 ? __half2float(__ushort_as_half((unsigned short)(r2[j] & 0xFFFFu)))
+                                                    : __uint_as_float(r2[j])) + s_bias[BN / 2 + c0 + j];
+                        v[j] = silu(v[j] + s_bias[c0 + j]) * x2;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += s_bias[c0 + j];
+                    if (g.act == 1) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                    }
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int col = n0 + c0 + q * 8;
+                        if (col < g.n_out) {  // n_out % 8 == 0: a group of 8 is all in or all out
+                            if (!SWIGLU && r_row != nullptr) {
+                                const uint4 rv = *reinterpret_cast<const uint4*>(r_row + col);
+                                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 rf = __half22float2(rh[j]);
+                                    v[q * 8 + 2 * j] = fmaf(s_gamma[c0 + q * 8 + 2 * j], v[q * 8 + 2 * j], rf.x);
+                                    v[q * 8 + 2 * j + 1] = fmaf(s_gamma[c0 + q * 8 + 2 * j + 1], v[q * 8 + 2 * j + 1], rf.y);
+                                }
+                            }
+                            uint4 o;
+                            o.x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
+                            o.y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
+                            o.z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
+                            o.w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
+                            *reinterpret_cast<uint4*>(c_row + col) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc<2 * BN>(tmem_base);
+    }
+}
+
+template <int BN, bool SWIGLU>
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, GemmArgs g, cudaStream_t stream) {
+    using S = GemmSmem<BN>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = linear_umma_kernel<BN, SWIGLU>;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+        if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(linear_umma_kernel): %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
+    g.tiles_m = (g.M + BM - 1) / BM;
+    g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
+    const int tiles = g.tiles_m * g.tiles_n;
+    const int grid = tiles < num_sms() ? tiles : num_sms();
+    kern<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tw, g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel launch: %s", cudaGetErrorString(e));
+    return FBB_OK;
+}
+
+int launch_linear(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
+                  int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
+                  cudaStream_t stream) {
+    if (M == 0) return FBB_OK;
+    const bool swiglu = epilogue == FBB_EPI_SWIGLU;
+    GemmArgs g;
+    g.C = reinterpret_cast<__half*>(C);
+    g.bias = reinterpret_cast<const __half*>(bias);
+    g.res = reinterpret_cast<const __half*>(res);
+    g.gamma = res != nullptr ? reinterpret_cast<const __half*>(gamma) : nullptr;
+    g.M = (int)M;
+    g.N = N;
+    g.K = K;
+    g.n_out = swiglu ? N / 2 : N;
+    g.ldc = ldc;
+    g.ldr = ldr;
+    g.act = epilogue == FBB_EPI_GELU ? 1 : 0;
+    g.acc_f16 = accumulate == FBB_ACC_F16 ? 1 : 0;
+    g.tiles_m = g.tiles_n = 0;
+
+    // Tile width: 256 columns unless 128-column tiles fill the SMs with clearly fewer idle slots in the last wave.
+    const int sms = num_sms();
+    const int64_t tm = (M + BM - 1) / BM;
+    const int64_t t256 = tm * ((g.n_out + 255) / 256), t128 = tm * ((g.n_out + 127) / 128);
+    const double cost256 = (double)((t256 + sms - 1) / sms) * 2.0;
+    const double cost128 = (double)((t128 + sms - 1) / sms) * 1.15;
+    const bool use128 = !swiglu && (g.n_out <= 128 || cost128 < cost256);
+
+    CUtensorMap ta, tw;
+    uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M};
+    int64_t str_a[2] = {1, lda};
+    uint32_t box_a[2] = {BK, BM};
+    int st = make_tmap_f16(&ta, A, 2, dims_a, str_a, box_a);
+    if (st != FBB_OK) return st;
+    uint64_t dims_w[2] = {(uint64_t)K, (uint64_t)N};
+    int64_t str_w[2] = {1, ldw};
+    uint32_t box_w[2] = {BK, (uint32_t)(swiglu ? 128 : (use128 ? 128 : 256))};
+    st = make_tmap_f16(&tw, W, 2, dims_w, str_w, box_w);
+    if (st != FBB_OK) return st;
+
+    if (swiglu) return launch_variant<256, true>(ta, tw, g, stream);
+    if (use128) return launch_variant<128, false>(ta, tw, g, stream);
+    return launch_variant<256, false>(ta, tw, g, stream);
+}
+
+}  // namespace fbb

@@ -1,0 +1,39 @@
+// Host-side declarations shared by the translation units of libfastbb_b200.so (not part of the public ABI).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fastbb_b200.h"
+
+namespace fbb {
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? FBB_OK : (int)e; }
+
+// Records a thread-local message for fbb_last_error() and returns `status` unchanged.
+int fail(int status, const char* fmt, ...);
+
+// cuTensorMapEncodeTiled resolved through the runtime (no link-time dependency on libcuda); nullptr if unavailable.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// fp16 tensor map with 128-byte swizzle, zero fill outside the tensor. dims/strides innermost first; strides in
+// elements for dims 1..rank-1 (dim 0 is contiguous); box innermost first (box[0] must be 64 elements = 128 bytes).
+int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
+                  const uint32_t* box);
+
+int num_sms();  // SM count of the current device
+
+int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
+                     float eps, int in_dtype, int param_dtype, cudaStream_t stream);
+
+int launch_linear(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
+                  int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
+                  cudaStream_t stream);
+
+int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
+                   const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, cudaStream_t stream);
+
+}  // namespace fbb

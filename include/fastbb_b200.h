@@ -1,0 +1,103 @@
+/* fastbb_b200 — C ABI of the B200 (sm_100a) ViT block kernels.
+ *
+ * This is the boundary the host side (Python, ctypes.CDLL) crosses. In the reference the same boundary is
+ * ctypes -> libcuda with a kernel-name + signature-string table (fastbb/kernels.py:19-41 SIGNATURES,
+ * fastbb/kernels.py:118-133 Kernels.launch); here it is a plain shared library with one entry point per operator.
+ *
+ * Conventions
+ *  - every pointer is a device pointer in the caller's current CUDA context/device; nothing is allocated or freed by
+ *    the library on any of these calls, and no call synchronises except fbb_device_status();
+ *  - `stream` is a cudaStream_t passed as void* (0 = legacy default stream); work is only enqueued;
+ *  - all leading dimensions and strides are in ELEMENTS, not bytes;
+ *  - return value: 0 = success, < 0 = argument rejected on the host before any launch (FBB_ERR_*), > 0 = cudaError_t;
+ *    fbb_last_error() gives a thread-local message for the last non-zero status of the calling thread;
+ *  - thread-compatible: no mutable state is shared between calls.
+ */
+#ifndef FASTBB_B200_H_
+#define FASTBB_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FBB_VERSION 100 /* major*10000 + minor*100 + patch */
+
+enum fbb_status {
+    FBB_OK = 0,
+    FBB_ERR_NULL = -1,        /* a required pointer is null */
+    FBB_ERR_SHAPE = -2,       /* a size / leading dimension is not supported (see each function) */
+    FBB_ERR_ALIGN = -3,       /* a pointer or stride breaks the 16-byte rule */
+    FBB_ERR_ENUM = -4,        /* unknown dtype / epilogue / accumulate / variant code */
+    FBB_ERR_DRIVER = -5,      /* the CUDA driver entry point for tensor maps could not be resolved or failed */
+    FBB_ERR_DEVICE_WAIT = -6  /* fbb_device_status(): a kernel gave up a bounded wait (details in out[]) */
+};
+
+enum fbb_dtype { FBB_DTYPE_F16 = 0, FBB_DTYPE_BF16 = 1, FBB_DTYPE_F32 = 2 };
+
+/* epilogue of fbb_linear_f16 (applied in fp32 on the accumulator, in this order):
+ *   v = acc + bias[n]; v = act(v); out = res[m,n] + gamma[n] * v   (gamma null -> res + v; res null -> v)       */
+enum fbb_epilogue {
+    FBB_EPI_NONE = 0,  /* act = identity                                        (gemm.py act None / "none")     */
+    FBB_EPI_GELU = 1,  /* act = exact erf GELU                                  (gemm.py act "gelu")            */
+    FBB_EPI_SWIGLU = 2 /* W holds w12 = [x1 rows | x2 rows]; out[m,j] = silu(x1_j) * x2_j, j < N/2 (vit.py:139-141) */
+};
+
+enum fbb_accumulate {
+    FBB_ACC_F32 = 0, /* fp32 tensor-memory accumulator   (reference g0 and g3; gemm variants f32, c1, c2, c4) */
+    FBB_ACC_F16 = 1  /* fp16 tensor-memory accumulator   (reference g1, g2 except fc2; gemm variant h)        */
+};
+
+enum fbb_flash_variant {
+    FBB_FLASH_FF = 0, /* fp32 accumulate for Q.K^T and for P.V        (attention.py variant "ff") */
+    FBB_FLASH_FH = 1, /* fp32 Q.K^T, fp16-accumulated P.V per key block ("fh")                    */
+    FBB_FLASH_HH = 2  /* fp16 accumulate for both                      ("hh")                      */
+};
+
+/* Library version (FBB_VERSION of the build). */
+int fbb_version(void);
+
+/* Static text for a status code returned by any function below. */
+const char* fbb_status_string(int status);
+
+/* Message for the last non-zero status returned to the calling thread ("" if none). */
+const char* fbb_last_error(void);
+
+/* Synchronises the current device, copies the device status word into out[4] = {code, detail, block, count} and
+ * clears it. Returns FBB_OK when no kernel recorded an error, FBB_ERR_DEVICE_WAIT when one ran out of a bounded
+ * wait (its output is then undefined), or a cudaError_t. Meant for tests and debugging, never for the hot path. */
+int fbb_device_status(unsigned int out[4]);
+
+/* y[m, :] = LayerNorm(x[m, :]) * w + b, statistics in fp32, output fp16.
+ * Replaces: the nn.LayerNorm calls of fastbb/vit.py:114,126,130,139,159,166,170 (norm1 / norm2) and :184,241 (vit.norm).
+ * x: [M, C] of in_dtype with row stride ldx; y: [M, C] fp16 with row stride ldy; w, b: [C] of param_dtype or null.
+ * Requires C % 8 == 0, ldx % 8 == 0 (fp16/bf16) or % 4 (fp32), ldy % 8 == 0, 16-byte aligned pointers. */
+int fbb_layernorm_f16(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
+                      float eps, int in_dtype, int param_dtype, void* stream);
+
+/* C[M, Nout] = epilogue(A[M, K] . W[N, K]^T), fp16 operands, tcgen05 tensor cores.
+ * Replaces: F.linear / torch._addmm_activation / F.gelu / F.silu.mul_ / addcmul of fastbb/vit.py:114-143, and
+ * gemm.linear + gemm_tn_{f32,c1,c2,c4,h}_{128,256} of fastbb/gemm.py:30-63 and fastbb/fastbb_kernels.cu:323-446.
+ * A: row stride lda; W: nn.Linear layout [N, K] with row stride ldw; C: row stride ldc; res: [M, Nout] fp16 with row
+ * stride ldr or null; bias: [N] fp16 or null; gamma: [Nout] fp16 or null (only read when res is given).
+ * Nout = N, or N/2 for FBB_EPI_SWIGLU (res and gamma must then be null). C may alias res (same pointer and stride).
+ * Requires K % 8 == 0, N % 8 == 0 (N % 16 for SwiGLU), lda/ldw/ldc/ldr % 8 == 0, 16-byte aligned A, W, C, res. */
+int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
+                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
+                   void* stream);
+
+/* O = softmax(scale . Q K^T) V for head dimension 64, no mask, any sequence length N >= 1.
+ * Replaces: attention.attention + flash64_r{1,2}_{hh,fh,ff} (fastbb/attention.py:31-60,
+ * fastbb/fastbb_kernels.cu:58-312) and the F.scaled_dot_product_attention fallback of fastbb/vit.py:149-150.
+ * q, k, v, o: fp16, element (b, n, h, d) at ptr[b*sb + n*sn + h*sh + d] (d contiguous): e.g. the three unbound views
+ * of the packed [B, N, 3, H, 64] qkv GEMM output, and o as [B, N, H*64]. Strides must be multiples of 8 elements,
+ * pointers 16-byte aligned, scale > 0. */
+int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                    int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                    int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTBB_B200_H_ */
