@@ -1,0 +1,52 @@
+"""Flash attention for head_dim 64 on the tcgen05 tensor cores (kernel: csrc/flash64.cu).
+
+Same call signature as the reference's fastbb/attention.py:31 `attention`:
+
+attention(q, k, v, scale=None, out=None, variant="hh")
+    q, k, v: [B, N, H, 64] fp16 views (d contiguous, other strides multiples of 8 elements; e.g. the unbound packed qkv
+    GEMM output [B, N, 3, H, 64]); returns O as [B, N, H, 64] (contiguous -> .view(B, N, H*64), no transpose).
+variant: "hh" fp16-accumulate QK^T and PV (fastest), "fh" fp32 QK^T + fp16 PV, "ff" fp32 both.
+Small inputs run the same kernel with one 128-query tile per CTA instead of the reference's SDPA fallback
+(fastbb/vit.py:146-150); anything the kernel does not cover (other head dims, dtypes, strides, CPU tensors,
+scale <= 0) raises instead of falling back to torch (fastbb/attention.py:38-48).
+"""
+import torch
+
+from . import _lib
+from .layernorm import _on
+
+
+def _ok(t):
+    return (t.is_cuda and t.dtype == torch.float16 and t.dim() == 4 and t.shape[-1] == 64 and t.stride(-1) == 1
+            and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0)
+
+
+def attention(q, k, v, scale=None, out=None, variant="hh", rows=None):
+    """q, k, v [B, N, H, 64] -> [B, N, H, 64]. `rows` (the reference's CTA-height override) is accepted and ignored."""
+    B, N, H, D = q.shape
+    if out is not None and (out.shape != (*q.shape[:-1], v.shape[-1]) or out.device != q.device or out.dtype != q.dtype):
+        raise ValueError("out must match the attention output shape, dtype and device")
+    if variant not in _lib.FLASH_VARIANT:
+        raise ValueError(f"unsupported variant: {variant}")
+    if scale is None:
+        scale = D ** -0.5
+    if not scale > 0:
+        raise ValueError("scale must be > 0")
+    if not (_ok(q) and _ok(k) and _ok(v) and k.shape == q.shape and v.shape == q.shape and k.device == q.device == v.device
+            and (out is None or _ok(out))):
+        raise ValueError("attention needs CUDA fp16 [B, N, H, 64] tensors with a contiguous last dim, strides that are "
+                         "multiples of 8 elements and 16-byte aligned storage (there is no fallback path)")
+    if out is None:
+        out = torch.empty((B, N, H, D), device=q.device, dtype=q.dtype)
+    with _on(q.device):
+        _lib.check(_lib.load().fbb_flash64_f16(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, N, H,
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+            float(scale), _lib.FLASH_VARIANT[variant], _lib.stream_ptr(q.device)))
+    return out
+
+
+def attention_bhnd(q, k, v, scale=None, variant="hh"):
+    """SDPA-layout drop-in: q, k, v [B, H, N, 64] -> [B, H, N, 64] (strided views, no copies)."""
+    return attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale, variant=variant).transpose(1, 2)
