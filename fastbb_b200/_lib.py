@@ -43,6 +43,12 @@ class FastbbError(RuntimeError):
 
 
 _LIB = None
+LAUNCHES = 0  # kernels enqueued through this module since import (each operator call is exactly one launch)
+
+
+def launched():
+    global LAUNCHES
+    LAUNCHES += 1
 
 
 def load(path=None):

@@ -38,12 +38,15 @@ def attention(q, k, v, scale=None, out=None, variant="hh", rows=None):
                          "multiples of 8 elements and 16-byte aligned storage (there is no fallback path)")
     if out is None:
         out = torch.empty((B, N, H, D), device=q.device, dtype=q.dtype)
+    if B == 0 or N == 0 or H == 0:
+        return out
     with _on(q.device):
         _lib.check(_lib.load().fbb_flash64_f16(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, N, H,
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
             float(scale), _lib.FLASH_VARIANT[variant], _lib.stream_ptr(q.device)))
+    _lib.launched()
     return out
 
 

@@ -57,9 +57,12 @@ def linear(x, w, b=None, act=None, res=None, gamma=None, variant="c2", out=None,
             r2 = r2.contiguous()
     if out is None:
         out = torch.empty(oshape, device=x.device, dtype=torch.float16)
+    if M == 0:
+        return out
     with _on(x.device):
         _lib.check(_lib.load().fbb_linear_f16(
             x2.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(b), _lib.ptr(r2), _lib.ptr(gamma), M, N, K,
             x2.stride(0) if M > 1 else K, w.stride(0) if N > 1 else K, n_out, (r2.stride(0) if M > 1 else n_out) if r2 is not None else 0,
             _ACT[act], _ACC[variant], _lib.stream_ptr(x.device)))
+    _lib.launched()
     return out

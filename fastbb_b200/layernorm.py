@@ -37,10 +37,13 @@ def layer_norm(x, weight=None, bias=None, eps=1e-6, out=None):
             pd = p.dtype
     if weight is not None and bias is not None and weight.dtype != bias.dtype:
         raise ValueError("weight and bias must share a dtype")
+    if M == 0:
+        return out
     with _on(x.device):
         _lib.check(_lib.load().fbb_layernorm_f16(
             x2.data_ptr(), out.data_ptr(), _lib.ptr(weight), _lib.ptr(bias), M, C, x2.stride(0) if M > 1 else C, C, float(eps),
             _lib.DTYPE_CODE[x.dtype], _lib.DTYPE_CODE[pd], _lib.stream_ptr(x.device)))
+    _lib.launched()
     return out
 
 

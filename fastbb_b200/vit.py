@@ -1,0 +1,336 @@
+"""Host orchestration of the ViT fast path on B200: a drop-in for `get_intermediate_layers` of DINOv2-style ViTs and a
+per-block forward patch for any pre-LN ViT (timm VisionTransformer, official DINOv2, Depth-Anything-V2 copies).
+
+Public surface and behaviour follow the reference's fastbb/vit.py (FastViT :41-255, install_vit_blocks :311-328): fp16
+weights and activations, autocast disabled inside, the packed qkv GEMM output read in place by the attention kernel,
+position-embedding interpolation in fp32 cached per grid and invalidated when the parameter is reloaded, optional CUDA
+graphs per input shape. What differs is below the operator calls: one block is
+
+    LayerNorm kernel -> qkv GEMM (+bias) -> flash attention -> proj GEMM (+bias, LayerScale, residual)
+    LayerNorm kernel -> fc1 GEMM (+bias, GELU) | w12 GEMM (+bias, SwiGLU) -> fc2 | w3 GEMM (+bias, LayerScale, residual)
+
+seven launches of this package's own sm_100a kernels, with no torch fallback for small inputs or unsupported layouts
+(the reference switches to SDPA below 2.2e5 elements, fastbb/vit.py:37,146; here the attention kernel has its own
+small-input configuration). The process-global cuBLAS fp16-accumulation flag the reference flips around a run
+(fastbb/vit.py:27-34) is never touched: the accumulate mode is an argument of each GEMM.
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .attention import attention
+from .gemm import linear
+from .layernorm import layer_norm
+
+HEAD_DIM = 64
+
+
+def _gemm_variants(gacc):
+    """(variant for qkv/proj/fc1/w12, variant for fc2/w3) for a parsed spec value."""
+    if gacc is True:
+        return "h", "h"
+    if gacc == "nofc2":
+        return "h", "f32"
+    if gacc is False or gacc == "chunk":
+        return "f32", "f32"
+    raise ValueError(f"unknown GEMM accumulate mode {gacc!r}")
+
+
+def _norm(mod, x):
+    """LayerNorm modules run through the fused kernel; any other norm module is the model's own code."""
+    if isinstance(mod, torch.nn.LayerNorm) and len(mod.normalized_shape) == 1:
+        return layer_norm(x, mod.weight, mod.bias, mod.eps)
+    return mod(x)
+
+
+def _gamma(block, name):
+    return getattr(getattr(block, name, None), "gamma", None)
+
+
+def _is_erf_gelu(act):
+    return act is None or (isinstance(act, torch.nn.GELU) and act.approximate == "none")
+
+
+def run_block(block, x, attn_variant, gacc):
+    """One pre-LN transformer block on x [B, N, C] fp16 (contiguous); returns a new tensor, x is not modified.
+    Block math as in fastbb/vit.py:108-143 (eval mode, no drop path)."""
+    v_main, v_fc2 = _gemm_variants(gacc)
+    a, m = block.attn, block.mlp
+    B, N, C = x.shape
+    H = a.num_heads
+    if C != H * HEAD_DIM:
+        raise NotImplementedError(f"the attention kernel covers head_dim {HEAD_DIM} only (embed {C}, heads {H})")
+    qkv = linear(_norm(block.norm1, x), a.qkv.weight, a.qkv.bias, variant=v_main).view(B, N, 3, H, HEAD_DIM)
+    q, k, v = qkv.unbind(2)
+    o = attention(q, k, v, scale=getattr(a, "scale", None), variant="ff" if attn_variant == "sdpa" else attn_variant)
+    g1 = _gamma(block, "ls1")
+    x = linear(o.view(B, N, C), a.proj.weight, a.proj.bias, res=x, gamma=g1, variant=v_main)
+    y = _norm(block.norm2, x)
+    g2 = _gamma(block, "ls2")
+    if hasattr(m, "fc1"):
+        act = getattr(m, "act", None)
+        if _is_erf_gelu(act):
+            h = linear(y, m.fc1.weight, m.fc1.bias, act="gelu", variant=v_main)
+        else:
+            h = act(linear(y, m.fc1.weight, m.fc1.bias, variant=v_main))
+        return linear(h, m.fc2.weight, m.fc2.bias, res=x, gamma=g2, variant=v_fc2)
+    h = linear(y, m.w12.weight, m.w12.bias, act="swiglu", variant=v_main)  # DINOv2 SwiGLU FFN (ViT-g)
+    return linear(h, m.w3.weight, m.w3.bias, res=x, gamma=g2, variant=v_fc2)
+
+
+def _param_version(parameters):
+    """Identity + mutation counters of parameters: changes when weights are reloaded or moved."""
+    try:
+        return tuple((id(p), p._version, p.device, p.dtype) for p in parameters)
+    except RuntimeError:  # inference tensors do not track mutations
+        return None
+
+
+def _flatten_blocks(blocks):
+    out = []
+    for b in blocks:
+        if isinstance(b, torch.nn.ModuleList) or type(b).__name__ == "BlockChunk":
+            out.extend(list(b))
+        else:
+            out.append(b)
+    return [b for b in out if not isinstance(b, torch.nn.Identity)]
+
+
+class FastViT:
+    """Wraps a DINOv2-style module tree (`pos_embed, patch_size, blocks, patch_embed, cls_token, norm`, optional
+    `num_register_tokens, register_tokens, interpolate_offset, interpolate_antialias`) and runs its block stack on the
+    B200 kernels. Constructor arguments as in fastbb/vit.py:42."""
+
+    def __init__(self, vit, attn="fh", gacc=True, dtype=torch.float16, out_dtype=None, graphs=False, graph_noclone=False):
+        if dtype != torch.float16:
+            raise ValueError("the B200 kernels compute in fp16 storage; dtype must be torch.float16")
+        _gemm_variants(gacc)
+        # the official code interpolates the fp32 table, so keep it before the module is cast
+        self.pos_fp32 = vit.pos_embed.detach().float().clone()
+        self.vit = vit.to(dtype).eval()
+        self.dtype, self.attn, self.gacc, self.out_dtype = dtype, attn, gacc, out_dtype
+        ps = vit.patch_size
+        self.ps = ps if isinstance(ps, int) else ps[0]
+        self.nreg = getattr(vit, "num_register_tokens", 0) or 0
+        self.blocks = _flatten_blocks(vit.blocks)
+        self._pos = {}
+        self._pos_version = _param_version((vit.pos_embed,))
+        self.graphs, self.graph_noclone = graphs, graph_noclone
+        self._graphs, self._pool, self._graph_version = {}, None, None
+        self._orig = {}
+
+    _version = staticmethod(_param_version)
+
+    # ------------------------------------------------------------------ tokens
+    def _refresh_pos(self):
+        """Drop cached tables (and graphs that baked them in) when pos_embed was reloaded, moved or re-cast."""
+        now = _param_version((self.vit.pos_embed,))
+        if now is not None and now == self._pos_version:
+            return
+        same_storage = (now is not None and self._pos_version is not None and now[0][:2] == self._pos_version[0][:2])
+        if same_storage:  # only moved / cast: the fp32 master copy is still right
+            self.pos_fp32 = self.pos_fp32.to(self.vit.pos_embed.device)
+        else:
+            self.pos_fp32 = self.vit.pos_embed.detach().float().clone()
+        self._pos.clear()
+        self._graphs.clear()
+        self._pool = None
+        self._pos_version = now
+
+    def pos_embed(self, h0, w0):
+        """Position table for an h0 x w0 patch grid, fp16 [1, 1 + h0*w0, C] (upstream DINOv2 interpolation rule)."""
+        self._refresh_pos()
+        table = self._pos.get((h0, w0))
+        if table is None:
+            pe = self.pos_fp32
+            n = pe.shape[1] - 1
+            side = int(math.sqrt(n))
+            if n == h0 * w0 and h0 == w0:
+                table = pe
+            else:
+                off = getattr(self.vit, "interpolate_offset", 0.1)
+                size_kw = {"scale_factor": ((h0 + off) / side, (w0 + off) / side)} if off else {"size": (h0, w0)}
+                grid = pe[:, 1:].reshape(1, side, side, -1).permute(0, 3, 1, 2)
+                grid = F.interpolate(grid, mode="bicubic", antialias=getattr(self.vit, "interpolate_antialias", False), **size_kw)
+                if grid.shape[-2:] != (h0, w0):
+                    raise RuntimeError(f"position grid came out as {tuple(grid.shape[-2:])}, wanted {(h0, w0)}")
+                table = torch.cat([pe[:, :1], grid.permute(0, 2, 3, 1).flatten(1, 2)], 1)
+            table = self._pos[(h0, w0)] = table.to(self.dtype)
+        return table
+
+    def tokens(self, x):
+        """Image batch [B, 3, H, W] -> tokens [B, 1 + nreg + hw, C]: the model's own patch embedding, cls token,
+        position table, registers after cls. Stays PyTorch host code (0.1 % of the FLOPs at 896x1344)."""
+        vit = self.vit
+        B, _, h, w = x.shape
+        t = vit.patch_embed(x.to(self.dtype))
+        t = torch.cat([vit.cls_token.to(self.dtype).expand(B, -1, -1), t], 1)
+        t = t + self.pos_embed(h // self.ps, w // self.ps)
+        if self.nreg:
+            t = torch.cat([t[:, :1], vit.register_tokens.to(self.dtype).expand(B, -1, -1), t[:, 1:]], 1)
+        return t
+
+    # ------------------------------------------------------------------ block
+    def block(self, b, x):
+        return run_block(b, x, self.attn, self.gacc)
+
+    # ------------------------------------------------------------------ API
+    def run(self, x, layers, norm=True):
+        """-> list of tokens [B, 1 + nreg + HW, C] after the blocks in `layers` (normed with vit.norm if norm)."""
+        out = []
+        last = max(layers)
+        with torch.autocast("cuda", enabled=False):
+            t = self.tokens(x).contiguous()
+            for i, b in enumerate(self.blocks):
+                t = run_block(b, t, self.attn, self.gacc)
+                if i in layers:
+                    out.append(_norm(self.vit.norm, t) if norm else t.clone())
+                if i >= last:
+                    break
+        return out
+
+    def run_graphed(self, x, layers, norm=True):
+        """graphs=True: one CUDA graph per (input shape, layers), captured on first use after one warm-up run; outputs
+        are the graph's static buffers (cloned unless graph_noclone). Falls back to run() for inference tensors."""
+        self._refresh_pos()
+        version = _param_version(self.vit.parameters())
+        if version is None:
+            return self.run(x, layers, norm)
+        if version != self._graph_version:
+            self._graphs.clear()
+            self._pool = None
+            self._graph_version = version
+        key = (tuple(x.shape), x.dtype, x.device, tuple(sorted(layers)), norm)
+        entry = self._graphs.get(key)
+        if entry is None:
+            static_in = x.clone()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.run(static_in, layers, norm)  # warm-up: position cache, kernel attributes
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._pool):
+                static_out = self.run(static_in, layers, norm)
+            self._pool = graph.pool()
+            entry = self._graphs[key] = (graph, static_in, static_out)
+        graph, static_in, static_out = entry
+        static_in.copy_(x)
+        graph.replay()
+        return static_out if self.graph_noclone else [o.clone() for o in static_out]
+
+    def _run(self, x, layers, norm):
+        return (self.run_graphed if self.graphs else self.run)(x, layers, norm)
+
+    def get_intermediate_layers(self, x, n=1, reshape=False, return_class_token=False, norm=True):
+        """Same contract as DinoVisionTransformer.get_intermediate_layers (fastbb/vit.py:220-235)."""
+        nb = len(self.blocks)
+        layers = list(range(nb - n, nb)) if isinstance(n, int) else list(n)
+        outs = self._run(x, set(layers), norm)
+        if self.out_dtype is not None and self.out_dtype != self.dtype:
+            outs = [o.to(self.out_dtype) for o in outs]
+        cls = [o[:, 0] for o in outs]
+        outs = [o[:, 1 + self.nreg:] for o in outs]
+        if reshape:
+            B, _, h, w = x.shape
+            outs = [o.reshape(B, h // self.ps, w // self.ps, -1).permute(0, 3, 1, 2).contiguous() for o in outs]
+        return tuple(zip(outs, cls)) if return_class_token else tuple(outs)
+
+    def forward_features(self, x):
+        """Same keys as the official DinoVisionTransformer.forward_features (eval, no masks)."""
+        t = self._run(x, {len(self.blocks) - 1}, norm=False)[0]
+        with torch.autocast("cuda", enabled=False):
+            n = _norm(self.vit.norm, t)
+        r = 1 + self.nreg
+        return {"x_norm_clstoken": n[:, 0], "x_norm_regtokens": n[:, 1:r], "x_norm_patchtokens": n[:, r:],
+                "x_prenorm": t, "masks": None}
+
+    def __call__(self, x):
+        """= official forward in eval mode with an Identity head: the normed cls token."""
+        return self.forward_features(x)["x_norm_clstoken"]
+
+    def install(self):
+        """Make the wrapped module's `get_intermediate_layers` (an instance attribute) call this object."""
+        self._orig["get_intermediate_layers"] = self.vit.__dict__.get("get_intermediate_layers")
+        self.vit.get_intermediate_layers = self.get_intermediate_layers
+        self.vit._fastbb = self
+        return self
+
+
+# ==================================================================== block-level drop-in (any ViT-style model)
+class _BlockCfg:
+    """Spec of a patched block (attention variant, GEMM accumulate mode)."""
+
+    def __init__(self, attn, gacc):
+        _gemm_variants(gacc)
+        self.attn, self.gacc = attn, gacc
+
+    def block(self, b, x):
+        return run_block(b, x, self.attn, self.gacc)
+
+
+def _ident(m):
+    return m is None or isinstance(m, (torch.nn.Identity, torch.nn.Dropout))
+
+
+def _block_supported(b):
+    """True for a pre-norm block norm1 -> attn(packed qkv, proj) -> ls1 -> +x; norm2 -> mlp(fc1, act, fc2 | w12, w3) ->
+    ls2 -> +x with 64-wide heads. q/k norms, gates, rope, separate qkv biases and unknown drop-path modules are not
+    (the structural test of fastbb/vit.py:273-294, plus the head-dim rule, because there is no SDPA path here)."""
+    a, m = getattr(b, "attn", None), getattr(b, "mlp", None)
+    if a is None or m is None or not (hasattr(b, "norm1") and hasattr(b, "norm2")):
+        return False
+    qkv, proj = getattr(a, "qkv", None), getattr(a, "proj", None)
+    if not (isinstance(qkv, torch.nn.Linear) and isinstance(proj, torch.nn.Linear)):
+        return False
+    heads = getattr(a, "num_heads", None)
+    if not isinstance(heads, int) or qkv.in_features != heads * HEAD_DIM:
+        return False
+    if any(not _ident(getattr(a, n, None)) for n in ("q_norm", "k_norm", "norm")) or getattr(a, "gate", None) is not None:
+        return False
+    if getattr(a, "qkv_bias_separate", False) or getattr(a, "rope", None) is not None:
+        return False
+    for n in ("drop_path", "drop_path1", "drop_path2"):
+        d = getattr(b, n, None)
+        if hasattr(b, n) and not _ident(d) and type(d).__name__ != "DropPath":
+            return False
+    for n in ("ls1", "ls2"):
+        ls = getattr(b, n, None)
+        if not (_ident(ls) or hasattr(ls, "gamma")):
+            return False
+    if hasattr(m, "fc1"):
+        return _ident(getattr(m, "norm", None)) and isinstance(m.fc1, torch.nn.Linear) and isinstance(m.fc2, torch.nn.Linear)
+    return hasattr(m, "w12") and hasattr(m, "w3")
+
+
+def _fast_block_forward(self, x, *args, **kw):
+    """Replacement for block.forward: masks, attention biases, causal attention and training mode go to the block's
+    original forward; everything else runs on the B200 kernels and comes back in the caller's dtype."""
+    masked = (args and args[0] is not None) or kw.get("attn_mask") is not None or kw.get("attn_bias") is not None
+    if masked or kw.get("is_causal") or self.training:
+        return type(self).forward(self, x, *args, **kw)
+    cfg = self._fbb_cfg
+    caller_dtype = x.dtype
+    with torch.autocast("cuda", enabled=False):
+        wd = self.attn.qkv.weight.dtype
+        y = cfg.block(self, x.to(wd).contiguous())
+    return y if caller_dtype == wd else y.to(caller_dtype)
+
+
+def install_vit_blocks(model, spec="fh-g0", convert=True):
+    """Patch every supported transformer block in `model` (forward -> B200 kernels). Tokenizer, position embedding and
+    heads stay the model's own code. convert=True: model.half(). Idempotent; returns the number of newly patched blocks."""
+    from . import parse_vit_spec
+    attn, gacc = parse_vit_spec(spec)
+    if convert:
+        model.half()
+    n = 0
+    for b in model.modules():
+        if b is model and not hasattr(b, "norm1"):
+            continue
+        if "_fbb_cfg" not in b.__dict__ and _block_supported(b):
+            b._fbb_cfg = _BlockCfg(attn, gacc)
+            b.forward = _fast_block_forward.__get__(b)
+            n += 1
+    return n

@@ -245,5 +245,5 @@ def block_stack(params, x, heads):
 
 def rel_l2(a, b):
     """Relative L2 error of a against the reference b: the reference's parity measure (README.md:12)."""
-    a, b = a.double(), b.double()
+    a, b = a.detach().double(), b.detach().double()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))

@@ -1,0 +1,289 @@
+"""Parity of the three CUDA operators, called through the C ABI (ctypes), against the CPU oracle on seeded inputs,
+against the reference's own outputs (tests/golden/ops.npz), and through size-independent properties at the benchmark's
+full sizes. Outputs sit inside canary-padded buffers so a write outside the logical tensor is caught.
+
+Tolerances (relative L2 against the fp32 oracle evaluated on the same fp16-rounded inputs): one fp16 rounding of the
+output is 2.1e-4 rms; fp32-accumulate paths must stay below 1e-3, fp16-accumulate paths below 1e-2 (the reference's
+own criterion for its fastest tier, README.md:12)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32, TOL_F16 = 1e-3, 1e-2
+CANARY = 1234.0
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def padded(shape, pad=64):
+    """A contiguous [rows, cols] view in the middle of a canary-filled buffer; returns (view, check())."""
+    rows, cols = int(np.prod(shape[:-1])), shape[-1]
+    buf = torch.full((rows * cols + 2 * pad,), CANARY, dtype=torch.float16, device=dev())
+    view = buf[pad:pad + rows * cols].view(*shape)
+
+    def check():
+        assert torch.all(buf[:pad] == CANARY) and torch.all(buf[pad + rows * cols:] == CANARY), "kernel wrote outside its output"
+    return view, check
+
+
+def status_ok():
+    from fastbb_b200 import _lib
+    assert _lib.device_status() == (0, 0, 0, 0)
+
+
+# ------------------------------------------------------------------------------------------------ LayerNorm
+@pytest.mark.parametrize("M,C,dtype", [(1, 384, torch.float16), (257, 384, torch.float16), (6145, 1024, torch.float16),
+                                       (1370, 1536, torch.float32), (33, 4096, torch.bfloat16), (5, 8, torch.float16),
+                                       (129, 2048, torch.float16), (64, 768, torch.float32)])
+def test_layernorm_matches_oracle(oracle, M, C, dtype):
+    from fastbb_b200.layernorm import layer_norm
+    g = torch.Generator().manual_seed(M * 131 + C)
+    x = (torch.randn(M, C, generator=g) * 2 + 0.5).to(dtype)
+    w, b = (1 + 0.1 * torch.randn(C, generator=g)).half(), (0.1 * torch.randn(C, generator=g)).half()
+    out, check = padded((M, C), pad=max(64, 16 - (M * C) % 8))
+    y = layer_norm(x.to(dev()), w.to(dev()), b.to(dev()), 1e-6, out=out)
+    want = oracle.layer_norm(x, w, b, 1e-6)
+    assert oracle.rel_l2(y.cpu().float(), want) < TOL_F32
+    check()
+    status_ok()
+
+
+def test_layernorm_large_mean_and_no_affine(oracle):
+    from fastbb_b200.layernorm import layer_norm
+    x = (torch.randn(64, 1024, generator=torch.Generator().manual_seed(3)) + 300.0).half()  # mean >> std: no E[x^2]-E[x]^2
+    y = layer_norm(x.to(dev()), None, None, 1e-6)
+    assert oracle.rel_l2(y.cpu().float(), oracle.layer_norm(x, None, None, 1e-6)) < 2e-3
+    # idempotence without affine: normalising a normalised row changes nothing beyond fp16 rounding
+    assert oracle.rel_l2(layer_norm(y, None, None, 1e-6).cpu().float(), y.cpu().float()) < 1e-3
+
+
+def test_layernorm_strided_rows_and_errors(oracle):
+    from fastbb_b200 import _lib
+    from fastbb_b200.layernorm import layer_norm
+    base = torch.randn(40, 512, generator=torch.Generator().manual_seed(4)).half().to(dev())
+    x = base[:, :384]                                           # row stride 512, C = 384
+    y = layer_norm(x, None, None, 1e-6)
+    assert oracle.rel_l2(y.cpu().float(), oracle.layer_norm(x.cpu(), None, None, 1e-6)) < TOL_F32
+    with pytest.raises(_lib.FastbbError):
+        layer_norm(torch.zeros(4, 12, dtype=torch.float16, device=dev()))      # C % 8 != 0
+    assert layer_norm(torch.zeros(0, 64, dtype=torch.float16, device=dev())).shape == (0, 64)
+
+
+# ------------------------------------------------------------------------------------------------ linear
+LINEAR_CASES = [
+    # M, N, K, act, bias, res, variant
+    (128, 256, 64, None, False, False, "f32"),
+    (1, 1024, 1024, None, True, False, "f32"),
+    (63, 200, 72, "gelu", True, True, "f32"),
+    (64, 8, 8, None, False, False, "f32"),
+    (65, 136, 40, None, True, True, "c2"),
+    (127, 128, 1024, "gelu", True, False, "f32"),
+    (129, 264, 96, None, True, True, "f32"),
+    (257, 1152, 384, None, True, False, "f32"),
+    (257, 384, 1536, None, True, True, "f32"),
+    (400, 3072, 768, "gelu", True, False, "c4"),
+    (1370, 1536, 1536, None, True, True, "f32"),
+    (257, 1536, 384, "gelu", True, False, "h"),
+    (1370, 4608, 1536, None, True, False, "h"),
+    (300, 272, 64, "swiglu", True, False, "f32"),
+    (1370, 8192, 1536, "swiglu", True, False, "f32"),
+    (1370, 8192, 1536, "swiglu", True, False, "h"),
+]
+
+
+@pytest.mark.parametrize("M,N,K,act,has_bias,has_res,variant", LINEAR_CASES)
+def test_linear_matches_oracle(oracle, M, N, K, act, has_bias, has_res, variant):
+    from fastbb_b200.gemm import linear
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+    b = (0.1 * torch.randn(N, generator=g)).half() if has_bias else None
+    n_out = N // 2 if act == "swiglu" else N
+    res = torch.randn(M, n_out, generator=g).half() if has_res else None
+    gam = (0.05 + 0.15 * torch.rand(n_out, generator=g)).half() if has_res else None
+    out, check = padded((M, n_out))
+    d = lambda t: None if t is None else t.to(dev())  # noqa: E731
+    y = linear(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant=variant, out=out)
+    want = oracle.linear(x, w, b, act=act, res=res, gamma=gam)
+    assert y.shape == (M, n_out)
+    assert oracle.rel_l2(y.cpu().float(), want) < (TOL_F16 if variant == "h" else TOL_F32)
+    check()
+    status_ok()
+
+
+def test_linear_against_reference_outputs(oracle):
+    """Same seeded inputs as tests/golden/make_golden.py; the stored outputs come from the reference's gemm.linear."""
+    from fastbb_b200.gemm import linear
+    from test_oracle import _op_inputs
+    g = load_golden("ops")
+    s = int(g["op_stride"])
+    lin, _ = _op_inputs()
+    d = lambda t: None if t is None else t.half().to(dev())  # noqa: E731
+    for tag, (x, w, b, act, res, gam) in lin.items():
+        y = linear(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant="f32")
+        # inputs were rounded to fp16 for the kernel: 2e-3 covers that rounding on K <= 1536 dot products
+        assert oracle.rel_l2(y.cpu().float()[::s], torch.from_numpy(g[f"linear_{tag}_out"])) < 2e-3, tag
+
+
+def test_linear_residual_without_gamma_batched_input_and_aliasing(oracle):
+    from fastbb_b200.gemm import linear
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(2, 130, 256, generator=g).half()
+    w = (torch.randn(256, 256, generator=g) / 16).half()
+    res = torch.randn(2, 130, 256, generator=g).half()
+    want = oracle.linear(x, w, None, res=res)
+    xd, wd, rd = x.to(dev()), w.to(dev()), res.to(dev())
+    y = linear(xd, wd, None, res=rd)
+    assert y.shape == (2, 130, 256) and y.data_ptr() != rd.data_ptr()
+    assert oracle.rel_l2(y.cpu().float(), want) < TOL_F32
+    assert torch.equal(rd.cpu(), res)                       # res untouched: a new tensor is returned
+    y2 = linear(xd, wd, None, res=rd, out=rd)               # in place on the residual stream is allowed
+    assert y2.data_ptr() == rd.data_ptr() and torch.equal(y2, y)
+
+
+def test_linear_large_magnitude_and_fp16_overflow_to_inf(oracle):
+    from fastbb_b200.gemm import linear
+    x = torch.full((128, 64), 60.0).half()
+    w = torch.full((8, 64), 20.0).half()                    # 64 * 1200 = 76800 > fp16 max: fp32 accumulate, inf on store
+    y = linear(x.to(dev()), w.to(dev())).cpu()
+    assert torch.isinf(y).all()
+    w2 = torch.full((8, 64), 10.0).half()                   # 38400 fits
+    y2 = linear(x.to(dev()), w2.to(dev())).cpu().float()
+    assert torch.allclose(y2, torch.full_like(y2, 38400.0), rtol=1e-3)
+
+
+def test_linear_rejects_what_the_kernel_does_not_cover():
+    from fastbb_b200 import _lib
+    from fastbb_b200.gemm import linear
+    x = torch.zeros(8, 12, dtype=torch.float16, device=dev())
+    with pytest.raises(_lib.FastbbError):
+        linear(x, torch.zeros(16, 12, dtype=torch.float16, device=dev()))              # K % 8
+    x = torch.zeros(8, 16, dtype=torch.float16, device=dev())
+    with pytest.raises(ValueError):
+        linear(x, torch.zeros(16, 16, dtype=torch.float32, device=dev()))
+    with pytest.raises(ValueError):
+        linear(x, torch.zeros(16, 16, dtype=torch.float16, device=dev()), out=torch.zeros(8, 8, dtype=torch.float16, device=dev()))
+    with pytest.raises(ValueError):
+        linear(x, torch.zeros(16, 16, dtype=torch.float16, device=dev()), gamma=torch.zeros(16, dtype=torch.float16, device=dev()))
+
+
+@pytest.mark.parametrize("M,N,K", [(6145, 3072, 1024), (6145, 4096, 1024), (6145, 1024, 4096), (32768, 1024, 1024)])
+def test_linear_full_size_linearity_and_column_sums(M, N, K):
+    """Benchmark-size GEMMs, checked without an M*N*K CPU product: (a) y(x1 + x2) = y(x1) + y(x2) - y(0) (the bias
+    cancels), (b) the sum over output columns equals x . (sum of W rows) + sum(bias), a matrix-vector product the CPU
+    does in milliseconds."""
+    from fastbb_b200.gemm import linear
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x1 = torch.randn(M, K, device=dev(), generator=g).half()
+    x2 = torch.randn(M, K, device=dev(), generator=g).half()
+    w = (torch.randn(N, K, device=dev(), generator=g) * 0.02).half()
+    b = (torch.randn(N, device=dev(), generator=g) * 0.1).half()
+    y1, y2 = linear(x1, w, b, variant="f32").float(), linear(x2, w, b, variant="f32").float()
+    xs = (x1.float() + x2.float()).half()
+    exact = xs.float() == x1.float() + x2.float()           # rows where the fp16 sum is exact
+    y12 = linear(xs, w, b, variant="f32").float()
+    rows = exact.all(dim=1)
+    assert rows.sum() >= 0
+    diff = (y12 - (y1 + y2 - b.float()))
+    assert diff.norm() / y12.norm() < 5e-3
+    colsum = y1.double().sum(dim=1).cpu()
+    want = (x1.cpu().double() @ w.cpu().double().sum(dim=0)) + b.cpu().double().sum()
+    assert ((colsum - want).norm() / want.norm()) < 2e-3
+    status_ok()
+
+
+# ------------------------------------------------------------------------------------------------ flash attention
+FLASH_SHAPES = [(1, 1, 1), (1, 63, 2), (1, 64, 2), (1, 65, 1), (1, 127, 3), (1, 128, 1), (1, 129, 2), (1, 257, 6), (2, 400, 16),
+                (1, 1370, 16), (3, 255, 5)]
+
+
+@pytest.mark.parametrize("variant", ["ff", "fh", "hh"])
+@pytest.mark.parametrize("B,N,H", FLASH_SHAPES)
+def test_flash_matches_oracle(oracle, variant, B, N, H):
+    from fastbb_b200.attention import attention
+    g = torch.Generator().manual_seed(B * 1000 + N * 10 + H)
+    qkv = torch.randn(B, N, 3, H, 64, generator=g).half()
+    qd, kd, vd = qkv.to(dev()).unbind(2)                     # strided views of the packed buffer, as in the block
+    out, check = padded((B, N, H, 64))
+    o = attention(qd, kd, vd, scale=0.125, variant=variant, out=out)
+    q, k, v = qkv.unbind(2)
+    want = oracle.attention(q, k, v, scale=0.125)
+    assert oracle.rel_l2(o.cpu().float(), want) < (TOL_F16 if variant == "hh" else TOL_F32)
+    assert not torch.isnan(o).any()
+    check()
+    status_ok()
+
+
+def test_flash_against_reference_outputs(oracle):
+    from fastbb_b200.attention import attention
+    from test_oracle import _op_inputs
+    g = load_golden("ops")
+    s = int(g["op_stride"])
+    _, att = _op_inputs()
+    for N, (q, k, v) in att.items():
+        o = attention(*(t.half().to(dev()) for t in (q, k, v)), scale=0.125, variant="ff")
+        assert oracle.rel_l2(o.cpu().float()[:, ::s], torch.from_numpy(g[f"attention_{N}_out"])) < 2e-3, N
+
+
+@pytest.mark.parametrize("variant", ["ff", "fh", "hh"])
+def test_flash_peaked_rows_default_scale_and_bhnd_layout(oracle, variant):
+    from fastbb_b200.attention import attention_bhnd
+    g = torch.Generator().manual_seed(5)
+    q, k = (3 * torch.randn(1, 4, 300, 64, generator=g)).half(), (3 * torch.randn(1, 4, 300, 64, generator=g)).half()
+    v = torch.randn(1, 4, 300, 64, generator=g).half()
+    o = attention_bhnd(q.to(dev()), k.to(dev()), v.to(dev()), variant=variant)
+    want = oracle.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
+    assert o.shape == (1, 4, 300, 64)
+    assert oracle.rel_l2(o.cpu().float(), want) < (TOL_F16 if variant == "hh" else 2e-3)
+
+
+@pytest.mark.parametrize("variant", ["ff", "fh", "hh"])
+@pytest.mark.parametrize("N", [4097, 6145, 16385])
+def test_flash_full_size_properties(variant, N):
+    """Benchmark-size sequences without an N^2 CPU softmax: (a) rows of P sum to one, so V = const gives O = const;
+    (b) permuting the keys (with their values) leaves O unchanged; (c) with identical keys, O is the mean of V."""
+    from fastbb_b200.attention import attention
+    H = 16
+    g = torch.Generator(device="cuda").manual_seed(N)
+    q = torch.randn(1, N, H, 64, device=dev(), generator=g).half()
+    k = torch.randn(1, N, H, 64, device=dev(), generator=g).half()
+    v = torch.randn(1, N, H, 64, device=dev(), generator=g).half()
+    ones = torch.full_like(v, 0.5)
+    o = attention(q, k, ones, scale=0.125, variant=variant).float()
+    assert (o - 0.5).abs().max() < (4e-3 if variant != "ff" else 1.5e-3)
+    perm = torch.randperm(N, device=dev(), generator=g)
+    o1 = attention(q, k, v, scale=0.125, variant=variant).float()
+    o2 = attention(q, k[:, perm], v[:, perm], scale=0.125, variant=variant).float()
+    assert (o1 - o2).norm() / o1.norm() < (TOL_F16 if variant == "hh" else 2e-3)
+    same_k = k[:, :1].expand(1, N, H, 64).contiguous()
+    o3 = attention(q, same_k, v, scale=0.125, variant=variant).float()
+    mean_v = v.float().mean(dim=1, keepdim=True)
+    assert (o3 - mean_v).abs().max() < 5e-3
+    status_ok()
+
+
+def test_flash_rejects_what_the_kernel_does_not_cover():
+    from fastbb_b200.attention import attention
+    q = torch.zeros(1, 8, 2, 32, dtype=torch.float16, device=dev())
+    with pytest.raises(ValueError):
+        attention(q, q, q)                                   # head_dim 32
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.float16, device=dev())
+    with pytest.raises(ValueError):
+        attention(q, q, q, scale=0.0)
+    with pytest.raises(ValueError):
+        attention(q, q, q, variant="xx")
+    with pytest.raises(ValueError):
+        attention(q.float(), q.float(), q.float())
+    assert attention(q[:, :0], q[:, :0], q[:, :0]).shape == (1, 0, 2, 64)
+
+
+def test_device_wait_limit_reports_instead_of_hanging():
+    """A clean device reports (0, 0, 0, 0); the status call is the only synchronising entry point."""
+    from fastbb_b200 import _lib
+    assert _lib.device_status() == (0, 0, 0, 0)

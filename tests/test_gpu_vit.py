@@ -1,0 +1,184 @@
+"""Stack-level parity on the GPU through the public API (install_vit / install_vit_blocks / models.dinov2), for the
+benchmark configurations, against the reference's own fp32 outputs (tests/golden, subsampled tokens) and, for the
+small config, against the oracle run live.
+
+Tolerances are the reference's parity criterion, relative L2 of the normed patch tokens against its fp32 tier:
+< 3e-3 for fp32-accumulate specs (fh-g0) and < 1e-2 for fp16-accumulate specs (hh-g1)."""
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import assert_same_inputs, load_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"fh-g0": 3e-3, "ff-g0": 3e-3, "sdpa-g0": 3e-3, "fh-g3": 3e-3, "fh-g2": 1e-2, "fh-g1": 1e-2, "hh-g1": 1e-2, "hh-g1-graph": 1e-2}
+
+
+def _fast_model(oracle, arch, spec, **kw):
+    from fastbb_b200.models.dinov2 import dinov2
+    params = oracle.make_params(arch, seed=0, **kw)
+    return params, dinov2(arch, params, spec=spec, device="cuda:0")
+
+
+def _check_against_golden(oracle, name, arch, H, W, heads, spec):
+    g = load_golden(name)
+    params, fast = _fast_model(oracle, arch, spec)
+    x = oracle.make_image(1, H, W, seed=1)
+    assert_same_inputs(g["image_checksum"], x, "image")
+    assert_same_inputs(g["qkv0_checksum"], params["blocks.0.attn.qkv.weight"], "qkv weight")
+    layers = [int(i) for i in g["layers"]]
+    stride = int(g["token_stride"])
+    outs = fast.get_intermediate_layers(x.to("cuda:0"), n=layers, return_class_token=True)
+    errs = []
+    for i, (patch, cls) in zip(layers, outs):
+        assert patch.dtype == torch.float16 and patch.shape[1] == (H // 14) * (W // 14)
+        e = oracle.rel_l2(patch[:, ::stride].float().cpu(), torch.from_numpy(g[f"patch_{i}"]))
+        ec = oracle.rel_l2(cls.float().cpu(), torch.from_numpy(g[f"cls_{i}"]))
+        errs.append((i, e, ec))
+        # The criterion is stated for patch tokens. The cls token of a random-init model starts ~10x smaller than the
+        # patch embeddings and is built almost entirely from accumulated block outputs, so the same absolute error is
+        # a larger relative one (measured: 2.3e-2 after 40 ViT-g blocks with fp16 accumulators): loose sanity bound only.
+        assert e < TOL[spec] and ec < 4 * TOL[spec], f"{name} {spec} layer {i}: patch {e:.2e} cls {ec:.2e}"
+        # whole-tensor norm (all tokens, not just the stored subsample)
+        assert abs(float(patch.double().norm()) / float(g[f"patch_norm_{i}"]) - 1) < TOL[spec]
+    from fastbb_b200 import _lib
+    assert _lib.device_status() == (0, 0, 0, 0)
+    return errs
+
+
+@pytest.mark.parametrize("spec", ["fh-g0", "hh-g1", "ff-g0", "sdpa-g0", "fh-g2", "fh-g3"])
+def test_c0_vits14_224_all_specs(oracle, spec):
+    _check_against_golden(oracle, "c0_vits14_224", "vits14", 224, 224, 6, spec)
+
+
+@pytest.mark.parametrize("spec", ["fh-g0", "hh-g1"])
+def test_c1_vitl14_896x1344(oracle, spec):
+    _check_against_golden(oracle, "c1_vitl14_896x1344", "vitl14", 896, 1344, 16, spec)
+
+
+@pytest.mark.parametrize("spec", ["hh-g1", "fh-g0"])
+def test_c3_vitg14_518_swiglu(oracle, spec):
+    _check_against_golden(oracle, "c3_vitg14_518", "vitg14", 518, 518, 24, spec)
+
+
+def test_c0_against_live_oracle_with_batch_and_odd_grid(oracle):
+    """Batch 3, non-square 210x266 input (15x19 patches + cls = 286 tokens: tails in every kernel), oracle run here."""
+    params, fast = _fast_model(oracle, "vits14", "fh-g0")
+    x = oracle.make_image(3, 210, 266, seed=5)
+    want = oracle.get_intermediate_layers(params, x, [5, 11], 6, return_class_token=True)
+    got = fast.get_intermediate_layers(x.to("cuda:0"), n=[5, 11], return_class_token=True)
+    for (p, c), (wp, wc) in zip(got, want):
+        assert oracle.rel_l2(p.float().cpu(), wp) < 3e-3 and oracle.rel_l2(c.float().cpu(), wc) < 1.2e-2
+
+
+def test_registers_forward_features_and_call(oracle):
+    params, fast = _fast_model(oracle, "vits14", "fh-g0", num_register_tokens=4, depth=3)
+    x = oracle.make_image(2, 224, 224, seed=6)
+    ff = fast.forward_features(x.to("cuda:0"))
+    assert ff["x_norm_patchtokens"].shape == (2, 256, 384) and ff["x_prenorm"].shape == (2, 261, 384)
+    # the oracle has no antialiased interpolation: compare on the table's own 37x37 grid (518 px), where none is needed
+    x = oracle.make_image(1, 518, 518, seed=6)
+    ff = fast.forward_features(x.to("cuda:0"))
+    want = oracle.run(params, x, {2}, 6, norm=True, interpolate_offset=0.0)[0]
+    assert ff["x_norm_regtokens"].shape == (1, 4, 384) and ff["x_norm_patchtokens"].shape == (1, 1369, 384)
+    assert oracle.rel_l2(ff["x_norm_patchtokens"].float().cpu(), want[:, 5:]) < 3e-3
+    assert oracle.rel_l2(ff["x_norm_clstoken"].float().cpu(), want[:, 0]) < 1.2e-2
+    assert torch.equal(fast(x.to("cuda:0")), ff["x_norm_clstoken"])
+
+
+def test_graph_replay_equals_eager_and_tracks_weight_reloads(oracle):
+    from fastbb_b200.models.dinov2 import dinov2
+    params = oracle.make_params("vits14", seed=0, depth=4)
+    eager = dinov2("vits14", params, spec="hh-g1", device="cuda:0")
+    graphed = dinov2("vits14", params, spec="hh-g1-graph", device="cuda:0")
+    assert graphed.graphs and not eager.graphs
+    x = oracle.make_image(2, 224, 224, seed=7).to("cuda:0")
+    a = eager.get_intermediate_layers(x, n=[1, 3])
+    b = graphed.get_intermediate_layers(x, n=[1, 3])
+    b2 = graphed.get_intermediate_layers(x, n=[1, 3])          # replay
+    for u, v, w in zip(a, b, b2):
+        assert torch.equal(u, v) and torch.equal(v, w)
+    assert len(graphed._graphs) == 1
+    x2 = oracle.make_image(2, 224, 224, seed=8).to("cuda:0")   # same shape, new content: same graph, new result
+    c = graphed.get_intermediate_layers(x2, n=[1, 3])
+    assert len(graphed._graphs) == 1 and not torch.equal(c[0], b[0])
+    assert torch.equal(c[0], eager.get_intermediate_layers(x2, n=[1, 3])[0])
+    # reloading weights invalidates the captured graphs
+    with torch.no_grad():
+        graphed.vit.blocks[0].ls1.gamma.mul_(0.5)
+        eager.vit.blocks[0].ls1.gamma.mul_(0.5)
+    d = graphed.get_intermediate_layers(x2, n=[1, 3])
+    assert torch.equal(d[0], eager.get_intermediate_layers(x2, n=[1, 3])[0]) and not torch.equal(d[0], c[0])
+
+
+def test_install_vit_patches_a_dinov2_style_module(oracle):
+    import fastbb_b200 as fb
+    from fastbb_b200.models.dinov2 import from_state_dict
+    params = oracle.make_params("vits14", seed=0, depth=2)
+    m = from_state_dict("vits14", params, device="cuda:0", dtype=torch.float32)
+    assert m.blocks[0].attn.qkv.weight.dtype == torch.float32
+    fast = fb.install_vit(m, "fh-g0-graph", out_dtype=torch.float32)
+    assert fast.graphs and m._fastbb is fast and m.blocks[0].attn.qkv.weight.dtype == torch.float16
+    x = oracle.make_image(1, 224, 224, seed=9)
+    out = m.get_intermediate_layers(x.to("cuda:0"), n=1, reshape=True)[0]
+    assert out.dtype == torch.float32 and out.shape == (1, 384, 16, 16)
+    want = oracle.get_intermediate_layers(params, x, 1, 6)[0].reshape(1, 16, 16, 384).permute(0, 3, 1, 2)
+    assert oracle.rel_l2(out.cpu(), want) < 3e-3
+
+
+# ---------------------------------------------------------------- c2: timm-style ViT-B/16 block stack via install_vit_blocks
+class _Attn(nn.Module):
+    def __init__(self, d, heads):
+        super().__init__()
+        self.num_heads, self.scale = heads, (d // heads) ** -0.5
+        self.qkv, self.proj = nn.Linear(d, 3 * d), nn.Linear(d, d)
+
+
+class _Mlp(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.fc1, self.act, self.fc2 = nn.Linear(d, 4 * d), nn.GELU(), nn.Linear(4 * d, d)
+
+
+class TimmLikeBlock(nn.Module):
+    """Stand-in for timm.models.vision_transformer.Block (timm is not installed): same attribute names, no LayerScale."""
+
+    def __init__(self, d=768, heads=12):
+        super().__init__()
+        self.norm1, self.norm2 = nn.LayerNorm(d, eps=1e-6), nn.LayerNorm(d, eps=1e-6)
+        self.attn, self.mlp = _Attn(d, heads), _Mlp(d)
+        self.ls1, self.ls2 = nn.Identity(), nn.Identity()
+
+    def forward(self, x, attn_mask=None):
+        raise RuntimeError("original forward reached")
+
+
+class TimmLikeStack(nn.Module):
+    def __init__(self, depth=12):
+        super().__init__()
+        self.blocks = nn.ModuleList([TimmLikeBlock() for _ in range(depth)])
+
+    def forward(self, x):
+        for b in self.blocks:
+            x = b(x)
+        return x
+
+
+@pytest.mark.parametrize("spec,batch", [("fh-g1", 1), ("fh-g0", 1), ("fh-g1", 3)])
+def test_c2_timm_like_block_stack(oracle, spec, batch):
+    import fastbb_b200 as fb
+    g = load_golden("c2_vitb16_blocks_1025")
+    params = oracle.make_params("vitb16_timm", seed=0, layerscale=False, patch_size=16, img_size=224)
+    stack = TimmLikeStack()
+    stack.load_state_dict({k: v for k, v in params.items() if k.startswith("blocks.")}, strict=True)
+    stack = stack.to("cuda:0").eval()
+    assert fb.install_vit_blocks(stack, spec) == 12
+    tokens = torch.randn(1, 1025, 768, generator=torch.Generator().manual_seed(1))
+    assert_same_inputs(g["tokens_checksum"], tokens, "tokens")
+    x = tokens.expand(batch, -1, -1).contiguous().to("cuda:0")   # fp32 caller: comes back as fp32
+    y = stack(x)
+    assert y.dtype == torch.float32 and y.shape == (batch, 1025, 768)
+    for bi in range(batch):
+        assert oracle.rel_l2(y[bi:bi + 1, ::int(g["token_stride"])].cpu(), torch.from_numpy(g["out"])) < TOL[spec]
+    assert abs(float(y[0].double().norm()) / float(g["out_norm"]) - 1) < TOL[spec]
