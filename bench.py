@@ -127,7 +127,7 @@ def run_ours(args, rank, local_rank, world):
     from fastbb_b200 import _lib, attention as attn_mod, replicas
     from fastbb_b200 import vit as vit_mod
     from fastbb_b200.models.dinov2 import dinov2
-    from oracle import vit_oracle as O  # seeded synthetic weights and image only; nothing of the oracle is timed here
+    from fastbb_b200 import synthetic as O
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")

@@ -52,6 +52,12 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Warpgroup-wide register reallocation (all four warps of an aligned warpgroup execute the same one).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---------------------------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -253,11 +259,98 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Warp-collective forms: every lane of a converged warp executes the call, one elected lane issues the instruction.
+// Keeping the issuing code warp-uniform lets the compiler hold descriptors and addresses in uniform registers, which is
+// what keeps the per-instruction issue cost of a long UMMA sequence low.
+__device__ __forceinline__ void umma_ss_warp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xFFFFFFFF;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xFFFFFFFF;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_warp(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "elect.sync _|q, 0xFFFFFFFF;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n"
+        ::"r"(bar)
+        : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------- math
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two fp32 FMAs in one instruction (packed f32x2 pipe of sm_100): d = a * b + c element-wise.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x for a pair of values on the FMA / ALU pipes instead of the 16-lane-per-SM transcendental unit: round-to-nearest
+// range reduction with the 1.5 * 2^23 trick (the low mantissa bits of x + magic hold round(x)), a degree-3 polynomial for
+// 2^f on [-0.5, 0.5] (max relative error 7.5e-5, a quarter of one fp16 rounding), and the integer part added into the
+// exponent field. Inputs below -126 are clamped (the result is then ~1e-38, i.e. zero for the softmax).
+__device__ __forceinline__ float2 exp2_emulated(float2 x) {
+    const float kMagic = 12582912.0f;
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 xm = fadd2(x, make_float2(kMagic, kMagic));
+    const float2 n = fadd2(xm, make_float2(-kMagic, -kMagic));
+    const float2 f = ffma2(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = ffma2(f, make_float2(0.05517163872718811f, 0.05517163872718811f), make_float2(0.2426111251115799f, 0.2426111251115799f));
+    p = ffma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+    p = ffma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(xm.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(xm.y) << 23));
+    return p;
 }
 __device__ __forceinline__ uint32_t ex2_approx_h2(uint32_t x) {
     uint32_t y;

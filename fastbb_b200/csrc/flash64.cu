@@ -5,16 +5,23 @@
 //
 // One CTA owns NQ (1 or 2) tiles of 128 queries of one (batch, head) and walks the keys in blocks of 128:
 //   warp 0          TMA producer: Q tiles once, then K_j and V_j into a ring of stages (128-byte swizzle, zero fill)
-//   warp 1          UMMA issuer: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory; after the softmax group
-//                   has written P_t (fp16) back into tensor memory, PV_t = P_t V_j (A from tensor memory, V as the
-//                   MN-major B operand, 8 x K16) into a second tensor-memory region, from zero for every key block
-//   warps 2..5/6..9 softmax group t: one thread per query row (tcgen05.ld 32x32b gives a thread its whole row, so the
-//                   row maximum and row sum need no shuffles); running max / sum / O in fp32 registers, base-2
-//                   exponentials; O = O * exp2(m_old - m_new) + PV_t is applied one key block late so the P.V product
-//                   of block j overlaps the exponentials of block j+1. With NQ = 2 the two groups alternate on the
-//                   tensor core (S of one tile is computed while the other tile is in its softmax).
-// Variants (fastbb/attention.py:5-7): ff = fp32 accumulate for S and PV; fh = fp32 S, fp16-accumulated PV per key
-// block added into the fp32 O; hh = fp16 accumulate for both, exponentials on half2 pairs.
+//   warp 1          UMMA issuer: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory; once the softmax group
+//                   has written P_t (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the
+//                   MN-major B operand, 8 x K16); O_t stays in tensor memory (fp32) over all key blocks
+//   warps 4..7/8..11 softmax group t: one thread per query row (tcgen05.ld 32x32b hands a thread its whole row, so the
+//                   row maximum and the row sum need no shuffles). The whole 128-key row of S is loaded at once, the
+//                   maximum is taken with 3-input max, p = 2^(s*scale*log2e - m) with packed f32x2 FMAs.
+//                   The running maximum m is only raised when a block exceeds it by more than 2^8 (then O_t and the
+//                   running sum are rescaled in place, a rare event after the first blocks); otherwise P is taken
+//                   relative to the older maximum, which keeps it <= 256 and exactly as accurate in fp16.
+// With NQ = 2 the two groups alternate on the tensor core (S of one tile is computed while the other tile is in its
+// softmax). Variants (fastbb/attention.py:5-7) select the accumulate type of S: ff / fh -> fp32 S, hh -> fp16 S (an f16
+// tensor-memory accumulator, read back as half2 pairs); the softmax arithmetic is fp32 in both, as in the reference.
+// P.V accumulates in fp32 for every variant, because O lives in tensor memory across all key blocks: an fp16 accumulator
+// there would add N terms in fp16, where the reference's fh / hh only ever add 64 (one key block) before going to fp32.
+// The kernel is bound by the exponentials, not the tensor core: 128 x 128 of them per S tile against 16 results per
+// clock per SM from the transcendental unit is twice the time of the tile's two matrix products. A quarter of the
+// exponentials are therefore evaluated with a polynomial on the FMA pipes (exp2_emulated).
 #include "common.cuh"
 #include "internal.h"
 
@@ -24,22 +31,44 @@ constexpr int FQ = 128;       // queries per tile
 constexpr int FK = 128;       // keys per block
 constexpr int kKVStages = 4;
 constexpr int kTileBytes = 128 * 64 * 2;  // one [128 x 64] fp16 tile
+constexpr float kLazyMax = 8.0f;          // raise the running maximum only beyond 2^8
+// Which of every 8 consecutive key pairs get their exponentials from the polynomial on the FMA pipes (bit i = pair i):
+// the transcendental unit (16 results per clock per SM) is what bounds this kernel, the FMA pipes have slack.
+constexpr unsigned kEmuMask = 0x88u;      // pairs 3 and 7 of 8: 25 %
+// Register split of the 384-thread (NQ = 2) kernel. It is launched with 168 registers per thread (the most 12 warps can
+// get); setmaxnreg.inc WAITS until the CTA's own pool has the registers, so the split must fit in that pool or the
+// kernel never starts its softmax: 128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168.
+constexpr int kRegsCtl = 72, kRegsSoftmax = 216;
+static_assert(128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168, "setmaxnreg split exceeds the CTA's register pool");
 
 // tensor-memory columns
 constexpr uint32_t kColS = 0;      // S_t at kColS + t*128 (128 columns each)
-constexpr uint32_t kColP = 256;    // P_t at kColP + t*64 (fp16 pairs: 64 columns each)
-constexpr uint32_t kColPV = 384;   // PV_t at kColPV + t*64 (64 columns each)
+constexpr uint32_t kColO = 256;    // O_t at kColO + t*64 (fp32, 64 columns each)
+constexpr uint32_t kColP = 384;    // P_t at kColP + t*64 (fp16 pairs: 64 columns each)
 
 struct FlashSmem {
     static constexpr int kQOff = 0;                                  // NQ x 16 KB
     static constexpr int kKOff = 2 * kTileBytes;                     // stages x 16 KB
     static constexpr int kVOff = kKOff + kKVStages * kTileBytes;     // stages x 16 KB
     static constexpr int kBarOff = kVOff + kKVStages * kTileBytes;
-    // barriers: q_full, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_full[2], pv_empty[2]
-    static constexpr int kNumBars = 1 + 4 * kKVStages + 8;
+    // barriers: q_full, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], o_full[2]
+    static constexpr int kNumBars = 1 + 4 * kKVStages + 6;
     static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kBytes + 1024;
 };
+
+#ifdef FBB_FLASH_TRACE
+// Development aid: per-iteration clock stamps of one softmax warp (CTA 0, lane 0 of warps 4 and 8) and of the UMMA
+// issuer, written to a global buffer set through fbb_flash_trace_buffer(). Not compiled into the shipped library.
+__device__ long long* g_flash_trace = nullptr;
+#define FBB_TRACE(slot, j, k)                                                                                         \
+    do {                                                                                                              \
+        if (g_flash_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (j) < 64)                   \
+            g_flash_trace[((slot) * 64 + (j)) * 8 + (k)] = clock64();                                                   \
+    } while (0)
+#else
+#define FBB_TRACE(slot, j, k) do { } while (0)
+#endif
 
 struct FlashArgs {
     __half* o;
@@ -48,8 +77,8 @@ struct FlashArgs {
     float scale_log2;
 };
 
-template <int NQ, bool S16, bool PV16>
-__global__ void __launch_bounds__(64 + 128 * NQ, 1)
+template <int NQ, bool S16>
+__global__ void __launch_bounds__(128 + 128 * NQ, 1)
 flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FlashArgs a) {
     using S = FlashSmem;
@@ -65,8 +94,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto v_empty = [&](int s) { return bar0 + 8u * (1 + 3 * kKVStages + s); };
     auto s_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + t); };
     auto p_ready = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 2 + t); };
-    auto pv_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 4 + t); };
-    auto pv_empty = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 6 + t); };
+    auto o_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 4 + t); };
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + S::kBarOff + S::kNumBars * 8);
     volatile int* s_abort = reinterpret_cast<volatile int*>(gen + S::kBarOff + S::kNumBars * 8 + 4);
 
@@ -88,8 +116,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int t = 0; t < 2; ++t) {
             mbar_init(s_full(t), 1);
             mbar_init(p_ready(t), 4);
-            mbar_init(pv_full(t), 1);
-            mbar_init(pv_empty(t), 4);
+            mbar_init(o_full(t), 1);
         }
         *s_abort = 0;
         fence_barrier_init();
@@ -107,6 +134,10 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
+    // Warpgroup 0 holds the two single-thread roles (and two idle warps) and gives registers away; the softmax
+    // warpgroups take them: a softmax thread keeps a whole 128-key row of S in registers.
+    if (warp < 4) {
+    if constexpr (NQ == 2) setmaxnreg_dec<kRegsCtl>();
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -128,215 +159,204 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
-            const uint32_t idesc_qk = make_idesc_f16(FQ, FK, !S16, false, false);
-            const uint32_t idesc_pv = make_idesc_f16(FQ, 64, !PV16, false, true);
-            constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
-            auto issue_qk = [&](int t, int s) {
-                const uint64_t qd = smem_desc(base + S::kQOff + t * kTileBytes, desc_hi);
-                const uint64_t kd = smem_desc(base + S::kKOff + s * kTileBytes, desc_hi);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) umma_ss(tmem_base + kColS + t * 128, qd + 2u * k, kd + 2u * k, idesc_qk, k != 0);
-                umma_commit(s_full(t));
-            };
-            bool ok = mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100);
-            if (ok) ok = mbar_wait(k_full(0), 0, s_abort, DEV_TIMEOUT_TMA_FULL, 0);
-            if (ok) {
-                tc_fence_after();
-                for (int t = 0; t < NQ; ++t) issue_qk(t, 0);
-                umma_commit(k_empty(0));
-            }
-            int s = 0;
-            uint32_t ph = 0;
-            for (int j = 0; j < nkb && ok; ++j) {
-                const int sn = (s + 1 == kKVStages) ? 0 : s + 1;
-                const uint32_t phn = (s + 1 == kKVStages) ? ph ^ 1u : ph;
-                for (int t = 0; t < NQ && ok; ++t) {
-                    // PV_t(j) = P_t(j) . V_j
-                    if (!mbar_wait(p_ready(t), j & 1, s_abort, DEV_TIMEOUT_OTHER, 200 + t)) { ok = false; break; }
-                    if (j > 0 && !mbar_wait(pv_empty(t), (j - 1) & 1, s_abort, DEV_TIMEOUT_TMEM_EMPTY, t)) { ok = false; break; }
-                    if (t == 0 && !mbar_wait(v_full(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, 16 + s)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t vd = smem_desc(base + S::kVOff + s * kTileBytes, desc_hi);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        umma_ts(tmem_base + kColPV + t * 64, tmem_base + kColP + t * 64 + 8u * k, vd + 128u * k, idesc_pv, k != 0);
-                    umma_commit(pv_full(t));
-                    if (t == NQ - 1) umma_commit(v_empty(s));
-                    // S_t(j+1) = Q_t . K_{j+1}^T
-                    if (j + 1 < nkb) {
-                        if (t == 0 && !mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_qk(t, sn);
-                        if (t == NQ - 1) umma_commit(k_empty(sn));
-                    }
-                }
-                s = sn;
-                ph = phn;
-            }
+        // The whole warp runs this code (one elected lane issues each instruction): descriptors and tensor-memory
+        // addresses stay warp-uniform, so issuing the twelve UMMAs of a key block costs little more than the UMMAs.
+        const uint32_t idesc_qk = make_idesc_f16(FQ, FK, !S16, false, false);
+        const uint32_t idesc_pv = make_idesc_f16(FQ, 64, true, false, true);
+        constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
+        const uint64_t qd0 = smem_desc(base + S::kQOff, desc_hi);
+        const uint64_t kd0 = smem_desc(base + S::kKOff, desc_hi);
+        const uint64_t vd0 = smem_desc(base + S::kVOff, desc_hi);
+        auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
+        auto issue_qk = [&](int t, int s) {
+            const uint64_t qd = qd0 + (uint64_t)(t * (kTileBytes >> 4));
+            const uint64_t kd = kd0 + (uint64_t)(s * (kTileBytes >> 4));
+            const uint32_t d = tmem_base + kColS + t * 128;
+            umma_ss_warp(d, qd, kd, idesc_qk, 0u);
+            umma_ss_warp(d, qd + 2u, kd + 2u, idesc_qk, 1u);
+            umma_ss_warp(d, qd + 4u, kd + 4u, idesc_qk, 1u);
+            umma_ss_warp(d, qd + 6u, kd + 6u, idesc_qk, 1u);
+            umma_commit_warp(s_full(t));
+        };
+        bool ok = all_ok(mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100));
+        if (ok) ok = all_ok(mbar_wait(k_full(0), 0, s_abort, DEV_TIMEOUT_TMA_FULL, 0));
+        if (ok) {
+            tc_fence_after();
+            for (int t = 0; t < NQ; ++t) issue_qk(t, 0);
+            umma_commit_warp(k_empty(0));
         }
+        int s = 0;
+        uint32_t ph = 0;
+        for (int j = 0; j < nkb && ok; ++j) {
+            const int sn = (s + 1 == kKVStages) ? 0 : s + 1;
+            const uint32_t phn = (s + 1 == kKVStages) ? ph ^ 1u : ph;
+            const uint32_t acc0 = j != 0 ? 1u : 0u;
+            const uint64_t vd = vd0 + (uint64_t)(s * (kTileBytes >> 4));
+#pragma unroll
+            for (int t = 0; t < NQ; ++t) {
+                // O_t += P_t(j) . V_j   (P_t(j) ready also means: S_t(j) consumed and O_t rescaled if it had to be)
+                FBB_TRACE(2 + t, j, 0);
+                if (!all_ok(mbar_wait(p_ready(t), j & 1, s_abort, DEV_TIMEOUT_OTHER, 200 + t))) { ok = false; break; }
+                FBB_TRACE(2 + t, j, 1);
+                if (t == 0 && !all_ok(mbar_wait(v_full(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, 16 + s))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + kColO + t * 64, pa = tmem_base + kColP + t * 64;
+                umma_ts_warp(d, pa, vd, idesc_pv, acc0);
+#pragma unroll
+                for (int k = 1; k < 8; ++k) umma_ts_warp(d, pa + 8u * k, vd + 128u * k, idesc_pv, 1u);
+                if (t == NQ - 1) umma_commit_warp(v_empty(s));
+                FBB_TRACE(2 + t, j, 2);
+                if (j + 1 < nkb) {
+                    // S_t(j+1) = Q_t . K_{j+1}^T
+                    if (t == 0 && !all_ok(mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn))) { ok = false; break; }
+                    tc_fence_after();
+                    issue_qk(t, sn);
+                    if (t == NQ - 1) umma_commit_warp(k_empty(sn));
+                    FBB_TRACE(2 + t, j, 3);
+                } else {
+                    umma_commit_warp(o_full(t));
+                }
+            }
+            s = sn;
+            ph = phn;
+        }
+    }
     } else {
         // ------------------------------------------------------------------ softmax groups: one thread per query row
-        const int t = (warp - 2) >> 2;
+        if constexpr (NQ == 2) setmaxnreg_inc<kRegsSoftmax>();
+        const int t = (warp - 4) >> 2;
         const int quad = warp & 3;
-        const int row_in_tile = quad * 32 + lane;
-        const int row = q0 + t * FQ + row_in_tile;
+        const int row = q0 + t * FQ + quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint32_t tS = lane_addr + kColS + t * 128;
+        const uint32_t tO = lane_addr + kColO + t * 64;
         const uint32_t tP = lane_addr + kColP + t * 64;
-        const uint32_t tPV = lane_addr + kColPV + t * 64;
         const float sl = a.scale_log2;
-        float o[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, c_prev = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
 
-        auto accumulate_pv = [&](float c) {
-            // o = o * c + PV_t
-            if constexpr (PV16) {
-                uint32_t r[32];
-                tmem_ld32_pack16(tPV, r);  // 64 fp16 columns as 32 half2 pairs
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&r[i]));
-                    o[2 * i] = fmaf(o[2 * i], c, f.x);
-                    o[2 * i + 1] = fmaf(o[2 * i + 1], c, f.y);
-                }
-            } else {
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t r[32];
-                    tmem_ld32(tPV + 32u * half, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[32 * half + i] = fmaf(o[32 * half + i], c, __uint_as_float(r[i]));
-                }
-            }
-        };
-
         for (int j = 0; j < nkb; ++j) {
+            if (quad == 0) FBB_TRACE(t, j, 0);
             if (!mbar_wait(s_full(t), j & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, t)) { ok = false; break; }
             tc_fence_after();
-            if (j > 0) {
-                // S_t(j) was committed after PV_t(j-1) was issued, so PV_t(j-1) is complete; this wait returns at once.
-                if (!mbar_wait(pv_full(t), (j - 1) & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
-                tc_fence_after();
-                accumulate_pv(c_prev);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pv_empty(t));
-            }
+            if (quad == 0) FBB_TRACE(t, j, 1);
             const int key0 = j * FK;
             const bool tail = key0 + FK > a.N;
-            float sum = 0.f;
-            float m_new;
-            if (!S16) {
-                // ---- pass 1: row maximum
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tS + 32u * c, r);
-                    tmem_wait_ld();
-                    if (tail) {
+            // ---- load the whole row of S (fp32: 128 registers; fp16 accumulator: 64 registers of half2 pairs) and take
+            //      its maximum
+            constexpr int kRegs = S16 ? 64 : 128;
+            uint32_t r[kRegs];
+            float mx;
+            if constexpr (!S16) {
+                tmem_ld32(tS, r);
+                tmem_ld32(tS + 32, r + 32);
+                tmem_ld32(tS + 64, r + 64);
+                tmem_ld32(tS + 96, r + 96);
+                tmem_wait_ld();
+                if (tail) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (key0 + c * 32 + i < a.N) mx = fmaxf(mx, __uint_as_float(r[i]));
-                    } else {
+                    for (int i = 0; i < 128; ++i)
+                        if (key0 + i >= a.N) r[i] = 0xFF800000u;  // -inf
+                }
+                float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]), mx2 = __uint_as_float(r[2]), mx3 = __uint_as_float(r[3]);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                for (int i = 4; i < 128; i += 8) {
+                    mx0 = fmax3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    mx1 = fmax3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    if (i + 4 < 128) {
+                        mx2 = fmax3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                        mx3 = fmax3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                     }
                 }
-                m_new = fmaxf(m_run, mx * sl);
-                // ---- pass 2: p = 2^(s*sl - m), row sum in fp32, P as fp16 pairs back to tensor memory
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    uint32_t pk[16];
-                    tmem_ld32(tS + 32u * c, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), sl, -m_new));
-                        float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), sl, -m_new));
-                        if (tail) {
-                            if (key0 + c * 32 + 2 * i >= a.N) p0 = 0.f;
-                            if (key0 + c * 32 + 2 * i + 1 >= a.N) p1 = 0.f;
-                        }
-                        sum += p0 + p1;
-                        pk[i] = pack_h2(p0, p1);
-                    }
-                    tmem_st16(tP + 16u * c, pk);
-                }
+                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl;
             } else {
-                // ---- fp16 S: values arrive as half2 pairs (two neighbouring keys per register)
-                __half2 mx2 = __float2half2_rn(-INFINITY);
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32_pack16(tS + 64u * c, r);
-                    tmem_wait_ld();
+                tmem_ld32_pack16(tS, r);
+                tmem_ld32_pack16(tS + 64, r + 32);
+                tmem_wait_ld();
+                if (tail) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        __half2 v = *reinterpret_cast<const __half2*>(&r[i]);
-                        if (tail) {
-                            const int key = key0 + c * 64 + 2 * i;
-                            if (key >= a.N) v = __halves2half2(__float2half(-INFINITY), __high2half(v));
-                            if (key + 1 >= a.N) v = __halves2half2(__low2half(v), __float2half(-INFINITY));
-                        }
-                        mx2 = __hmax2(mx2, v);
+                    for (int i = 0; i < 64; ++i) {
+                        if (key0 + 2 * i >= a.N) r[i] = (r[i] & 0xFFFF0000u) | 0xFC00u;          // low half -> -inf
+                        if (key0 + 2 * i + 1 >= a.N) r[i] = (r[i] & 0x0000FFFFu) | 0xFC000000u;  // high half -> -inf
                     }
                 }
-                const float mx = fmaxf(__low2float(mx2), __high2float(mx2));
-                // keep the running maximum representable in fp16 so the half2 fma below subtracts exactly this value
-                m_new = fmaxf(m_run, __half2float(__float2half_rn(mx * sl)));
-                const __half2 sl2 = __float2half2_rn(sl);
-                const __half2 nm2 = __float2half2_rn(-m_new);
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32_pack16(tS + 64u * c, r);
-                    tmem_wait_ld();
+                __half2 mxa = *reinterpret_cast<const __half2*>(&r[0]), mxb = *reinterpret_cast<const __half2*>(&r[1]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const __half2 x = __hfma2(*reinterpret_cast<const __half2*>(&r[i]), sl2, nm2);
-                        uint32_t p = ex2_approx_h2(*reinterpret_cast<const uint32_t*>(&x));
-                        if (tail) {
-                            const int key = key0 + c * 64 + 2 * i;
-                            if (key >= a.N) p &= 0xFFFF0000u;
-                            if (key + 1 >= a.N) p &= 0x0000FFFFu;
-                        }
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p));
-                        sum += f.x + f.y;
-                        r[i] = p;
-                    }
-                    tmem_st32(tP + 32u * c, r);
+                for (int i = 2; i < 64; i += 2) {
+                    mxa = __hmax2(mxa, *reinterpret_cast<const __half2*>(&r[i]));
+                    mxb = __hmax2(mxb, *reinterpret_cast<const __half2*>(&r[i + 1]));
                 }
+                mxa = __hmax2(mxa, mxb);
+                mx = fmaxf(__low2float(mxa), __high2float(mxa)) * sl;
             }
+            if (quad == 0) FBB_TRACE(t, j, 2);
+            // ---- running maximum: raised only when this block exceeds it by more than 2^kLazyMax
+            if (j == 0) {
+                m_ref = mx;
+            } else if (__any_sync(0xffffffffu, mx > m_ref + kLazyMax)) {
+                const float m_new = fmaxf(m_ref, mx);
+                const float c = ex2_approx(m_ref - m_new);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + 32u * half, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * c);
+                    tmem_st32(tO + 32u * half, o);
+                }
+                l_run *= c;
+                m_ref = m_new;
+            }
+            // ---- p = 2^(s*sl - m) in fp32 for both accumulate types; kEmuEvery-th pair on the FMA pipes, the others on
+            //      the transcendental unit; row sum in fp32; P as fp16 pairs back to tensor memory
+            const float2 sl2 = make_float2(sl, sl), nm2 = make_float2(-m_ref, -m_ref);
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float2 sv;
+                    if constexpr (!S16) sv = make_float2(__uint_as_float(r[32 * c + 2 * i]), __uint_as_float(r[32 * c + 2 * i + 1]));
+                    else sv = __half22float2(*reinterpret_cast<const __half2*>(&r[16 * c + i]));
+                    const float2 x = ffma2(sv, sl2, nm2);
+                    float2 p;
+                    if ((kEmuMask >> (i & 7)) & 1) p = exp2_emulated(x);
+                    else p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                    if (i & 1) acc1 = fadd2(acc1, p); else acc0 = fadd2(acc0, p);
+                    pk[i] = pack_h2(p.x, p.y);
+                }
+                tmem_st16(tP + 16u * c, pk);
+            }
+            const float sum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+            if (quad == 0) FBB_TRACE(t, j, 3);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready(t));
-            c_prev = ex2_approx(m_run - m_new);
-            l_run = fmaf(l_run, c_prev, sum);
-            m_run = m_new;
+            if (quad == 0) FBB_TRACE(t, j, 4);
+            l_run += sum;
         }
-        if (ok && mbar_wait(pv_full(t), (nkb - 1) & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
+        if (ok && mbar_wait(o_full(t), 0, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
             tc_fence_after();
-            accumulate_pv(c_prev);
-            if (row < a.N) {
-                const float inv = 1.f / l_run;
-                __half* dst = a.o + (int64_t)b * a.o_sb + (int64_t)row * a.o_sn + (int64_t)h * a.o_sh;
+            const float inv = 1.f / l_run;
+            __half* dst = a.o + (int64_t)b * a.o_sb + (int64_t)row * a.o_sn + (int64_t)h * a.o_sh;
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    uint4 u;
-                    u.x = pack_h2(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
-                    u.y = pack_h2(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
-                    u.z = pack_h2(o[8 * v + 4] * inv, o[8 * v + 5] * inv);
-                    u.w = pack_h2(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + 8 * v) = u;
+            for (int half = 0; half < 2; ++half) {
+                uint32_t o[32];
+                tmem_ld32(tO + 32u * half, o);
+                tmem_wait_ld();
+                if (row < a.N) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 u;
+                        u.x = pack_h2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                        u.y = pack_h2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                        u.z = pack_h2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                        u.w = pack_h2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + 32 * half + 8 * v) = u;
+                    }
                 }
             }
         }
@@ -351,24 +371,31 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
 }
 
-template <int NQ, bool S16, bool PV16>
+template <int NQ, bool S16>
 static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashArgs& a, int B,
                                 cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = flash64_umma_kernel<NQ, S16, PV16>;
+    auto kern = flash64_umma_kernel<NQ, S16>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem::kDynamic);
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(flash64_umma_kernel): %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
     dim3 grid((unsigned)((a.N + FQ * NQ - 1) / (FQ * NQ)), (unsigned)(B * a.H), 1);
-    kern<<<grid, 64 + 128 * NQ, FlashSmem::kDynamic, stream>>>(tq, tk, tv, a);
+    kern<<<grid, 128 + 128 * NQ, FlashSmem::kDynamic, stream>>>(tq, tk, tv, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail((int)e, "flash64_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }
+
+#ifdef FBB_FLASH_TRACE
+extern "C" int fbb_flash_trace_buffer(void* buf) {
+    long long* p = reinterpret_cast<long long*>(buf);
+    return (int)cudaMemcpyToSymbol(g_flash_trace, &p, sizeof(p));
+}
+#endif
 
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
                    const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, cudaStream_t stream) {
@@ -397,15 +424,9 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
     // Small inputs: one 128-query tile per CTA so that more SMs get work (the small-token path).
     const int64_t ctas2 = (int64_t)((N + 2 * FQ - 1) / (2 * FQ)) * B * H;
     const bool two = ctas2 >= num_sms();
-#define FBB_FLASH_DISPATCH(S16, PV16)                                                         \
-    (two ? launch_flash_variant<2, S16, PV16>(tq, tk, tv, a, B, stream)                       \
-         : launch_flash_variant<1, S16, PV16>(tq, tk, tv, a, B, stream))
-    switch (variant) {
-        case FBB_FLASH_FF: return FBB_FLASH_DISPATCH(false, false);
-        case FBB_FLASH_FH: return FBB_FLASH_DISPATCH(false, true);
-        default: return FBB_FLASH_DISPATCH(true, true);
-    }
-#undef FBB_FLASH_DISPATCH
+    const bool s16 = variant == FBB_FLASH_HH;
+    if (two) return s16 ? launch_flash_variant<2, true>(tq, tk, tv, a, B, stream) : launch_flash_variant<2, false>(tq, tk, tv, a, B, stream);
+    return s16 ? launch_flash_variant<1, true>(tq, tk, tv, a, B, stream) : launch_flash_variant<1, false>(tq, tk, tv, a, B, stream);
 }
 
 }  // namespace fbb

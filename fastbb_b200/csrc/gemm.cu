@@ -121,34 +121,35 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_f16(BM, BN, !g.acc_f16, false, false);
-            constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
-            int s = 0;
-            uint32_t ph = 0;
-            int acc = 0;
-            uint32_t acc_ph = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, acc)) break;
+        // The whole warp runs this loop and one elected lane issues each instruction, so that descriptors and
+        // addresses are warp-uniform values (uniform registers) rather than per-thread arithmetic in a divergent branch.
+        const uint32_t idesc = make_idesc_f16(BM, BN, !g.acc_f16, false, false);
+        constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
+        const uint64_t adesc0 = smem_desc(base, desc_hi);
+        auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
+        int s = 0;
+        uint32_t ph = 0;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            if (!all_ok(mbar_wait(tempty_bar(acc), acc_ph ^ 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, acc))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!all_ok(mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, s))) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, s)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = base + s * S::kStageBytes;
-                    const uint64_t adesc = smem_desc(sa, desc_hi);
-                    const uint64_t bdesc = smem_desc(sa + S::kABytes, desc_hi);
+                const uint64_t adesc = adesc0 + (uint64_t)(s * (S::kStageBytes >> 4));
+                const uint64_t bdesc = adesc + (uint64_t)(S::kABytes >> 4);
+                umma_ss_warp(d_tmem, adesc, bdesc, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    umma_commit(empty_bar(s));  // stage reusable once these UMMAs have read it
-                    if (++s == kStages) { s = 0; ph ^= 1u; }
-                }
-                if (!ok) break;
-                umma_commit(tfull_bar(acc));  // accumulator complete
-                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+                for (int k = 1; k < BK / 16; ++k) umma_ss_warp(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, 1u);
+                umma_commit_warp(empty_bar(s));  // stage reusable once these UMMAs have read it
+                if (++s == kStages) { s = 0; ph ^= 1u; }
             }
+            if (!ok) break;
+            umma_commit_warp(tfull_bar(acc));  // accumulator complete
+            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
         }
     } else {
         // ------------------------------------------------------------------ epilogue (8 warps)

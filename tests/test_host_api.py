@@ -178,3 +178,13 @@ def test_arch_table_and_swiglu_width():
         g = DinoV2Params("vitg14")
     assert g.blocks[0].mlp.w12.weight.shape == (8192, 1536) and g.blocks[0].mlp.w3.weight.shape == (1536, 4096)
     assert g.pos_embed.shape == (1, 37 * 37 + 1, 1536)
+
+
+def test_synthetic_generator_matches_the_oracles(oracle):
+    """The package ships its own seeded generator for benchmarks; it must make the tensors the golden fixtures assume."""
+    from fastbb_b200 import synthetic
+    a, b = synthetic.make_params("vits14", seed=0, depth=2), oracle.make_params("vits14", seed=0, depth=2)
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    a, b = synthetic.make_params("vitg14", seed=3, depth=1, num_register_tokens=4), oracle.make_params("vitg14", seed=3, depth=1, num_register_tokens=4)
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    assert torch.equal(synthetic.make_image(2, 28, 42, seed=5), oracle.make_image(2, 28, 42, seed=5))
