@@ -5,9 +5,10 @@
 //
 // One CTA owns NQ (1 or 2) tiles of 128 queries of one (batch, head) and walks the keys in blocks of 128:
 //   warp 0          TMA producer: Q tiles once, then K_j and V_j into a ring of stages (128-byte swizzle, zero fill)
-//   warp 1          UMMA issuer: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory; once the softmax group
-//                   has written P_t (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the
-//                   MN-major B operand, 8 x K16); O_t stays in tensor memory (fp32) over all key blocks
+//   warps 1, 2      UMMA issuers, one per tile: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory, issued as
+//                   soon as the softmax group holds the previous S_t in registers; once the group has written P_t
+//                   (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the MN-major B operand,
+//                   8 x K16); O_t stays in tensor memory (fp32) over all key blocks
 //   warps 4..7/8..11 softmax group t: one thread per query row (tcgen05.ld 32x32b hands a thread its whole row, so the
 //                   row maximum and the row sum need no shuffles). The whole 128-key row of S is loaded at once, the
 //                   maximum is taken with 3-input max, p = 2^(s*scale*log2e - m) with packed f32x2 FMAs.
@@ -34,7 +35,10 @@ constexpr int kTileBytes = 128 * 64 * 2;  // one [128 x 64] fp16 tile
 constexpr float kLazyMax = 8.0f;          // raise the running maximum only beyond 2^8
 // Which of every 8 consecutive key pairs get their exponentials from the polynomial on the FMA pipes (bit i = pair i):
 // the transcendental unit (16 results per clock per SM) is what bounds this kernel, the FMA pipes have slack.
-constexpr unsigned kEmuMask = 0x88u;      // pairs 3 and 7 of 8: 25 %
+#ifndef FBB_EMU_MASK
+#define FBB_EMU_MASK 0x88u
+#endif
+constexpr unsigned kEmuMask = FBB_EMU_MASK;  // 0x88: pairs 3 and 7 of 8, 25 %
 // Register split of the 384-thread (NQ = 2) kernel. It is launched with 168 registers per thread (the most 12 warps can
 // get); setmaxnreg.inc WAITS until the CTA's own pool has the registers, so the split must fit in that pool or the
 // kernel never starts its softmax: 128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168.
@@ -51,8 +55,8 @@ struct FlashSmem {
     static constexpr int kKOff = 2 * kTileBytes;                     // stages x 16 KB
     static constexpr int kVOff = kKOff + kKVStages * kTileBytes;     // stages x 16 KB
     static constexpr int kBarOff = kVOff + kKVStages * kTileBytes;
-    // barriers: q_full, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], o_full[2]
-    static constexpr int kNumBars = 1 + 4 * kKVStages + 6;
+    // barriers: q_full, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_done[2], s_free[2]
+    static constexpr int kNumBars = 1 + 4 * kKVStages + 8;
     static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kBytes + 1024;
 };
@@ -94,7 +98,8 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto v_empty = [&](int s) { return bar0 + 8u * (1 + 3 * kKVStages + s); };
     auto s_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + t); };
     auto p_ready = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 2 + t); };
-    auto o_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 4 + t); };
+    auto pv_done = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 4 + t); };
+    auto s_free = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 6 + t); };
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + S::kBarOff + S::kNumBars * 8);
     volatile int* s_abort = reinterpret_cast<volatile int*>(gen + S::kBarOff + S::kNumBars * 8 + 4);
 
@@ -110,13 +115,14 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int s = 0; s < kKVStages; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(v_full(s), 1);
-            mbar_init(k_empty(s), 1);
-            mbar_init(v_empty(s), 1);
+            mbar_init(k_empty(s), NQ);  // one commit per tile issuer
+            mbar_init(v_empty(s), NQ);
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(s_full(t), 1);
             mbar_init(p_ready(t), 4);
-            mbar_init(o_full(t), 1);
+            mbar_init(pv_done(t), 1);
+            mbar_init(s_free(t), 4);
         }
         *s_abort = 0;
         fence_barrier_init();
@@ -157,66 +163,60 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             if (!ok) __nanosleep(20000);
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ UMMA issuer
-        // The whole warp runs this code (one elected lane issues each instruction): descriptors and tensor-memory
-        // addresses stay warp-uniform, so issuing the twelve UMMAs of a key block costs little more than the UMMAs.
+    } else if (warp - 1 < NQ) {
+        // ------------------------------------------------------------------ UMMA issuers: warp 1 for tile 0, warp 2 for tile 1
+        // Each tile has its own issuer so that neither tile ever waits for the other one's turn. The whole warp runs the
+        // code and one elected lane issues each instruction (descriptors and addresses stay warp-uniform).
+        // Per key block j the order follows the order in which the softmax group produces its events:
+        //   S_t free (the group has block j in registers)  ->  S_t(j+1) = Q_t K_{j+1}^T, issued while the group works on j
+        //   P_t(j) written                                  ->  O_t += P_t(j) V_j
+        const int t = warp - 1;
         const uint32_t idesc_qk = make_idesc_f16(FQ, FK, !S16, false, false);
         const uint32_t idesc_pv = make_idesc_f16(FQ, 64, true, false, true);
         constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
-        const uint64_t qd0 = smem_desc(base + S::kQOff, desc_hi);
+        const uint64_t qd = smem_desc(base + S::kQOff + t * kTileBytes, desc_hi);
         const uint64_t kd0 = smem_desc(base + S::kKOff, desc_hi);
         const uint64_t vd0 = smem_desc(base + S::kVOff, desc_hi);
+        const uint32_t dS = tmem_base + kColS + t * 128, dO = tmem_base + kColO + t * 64, aP = tmem_base + kColP + t * 64;
         auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
-        auto issue_qk = [&](int t, int s) {
-            const uint64_t qd = qd0 + (uint64_t)(t * (kTileBytes >> 4));
+        auto issue_qk = [&](int s) {
             const uint64_t kd = kd0 + (uint64_t)(s * (kTileBytes >> 4));
-            const uint32_t d = tmem_base + kColS + t * 128;
-            umma_ss_warp(d, qd, kd, idesc_qk, 0u);
-            umma_ss_warp(d, qd + 2u, kd + 2u, idesc_qk, 1u);
-            umma_ss_warp(d, qd + 4u, kd + 4u, idesc_qk, 1u);
-            umma_ss_warp(d, qd + 6u, kd + 6u, idesc_qk, 1u);
+            umma_ss_warp(dS, qd, kd, idesc_qk, 0u);
+            umma_ss_warp(dS, qd + 2u, kd + 2u, idesc_qk, 1u);
+            umma_ss_warp(dS, qd + 4u, kd + 4u, idesc_qk, 1u);
+            umma_ss_warp(dS, qd + 6u, kd + 6u, idesc_qk, 1u);
             umma_commit_warp(s_full(t));
+            umma_commit_warp(k_empty(s));
         };
         bool ok = all_ok(mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100));
         if (ok) ok = all_ok(mbar_wait(k_full(0), 0, s_abort, DEV_TIMEOUT_TMA_FULL, 0));
         if (ok) {
             tc_fence_after();
-            for (int t = 0; t < NQ; ++t) issue_qk(t, 0);
-            umma_commit_warp(k_empty(0));
+            issue_qk(0);
         }
         int s = 0;
         uint32_t ph = 0;
         for (int j = 0; j < nkb && ok; ++j) {
             const int sn = (s + 1 == kKVStages) ? 0 : s + 1;
             const uint32_t phn = (s + 1 == kKVStages) ? ph ^ 1u : ph;
-            const uint32_t acc0 = j != 0 ? 1u : 0u;
-            const uint64_t vd = vd0 + (uint64_t)(s * (kTileBytes >> 4));
-#pragma unroll
-            for (int t = 0; t < NQ; ++t) {
-                // O_t += P_t(j) . V_j   (P_t(j) ready also means: S_t(j) consumed and O_t rescaled if it had to be)
-                FBB_TRACE(2 + t, j, 0);
-                if (!all_ok(mbar_wait(p_ready(t), j & 1, s_abort, DEV_TIMEOUT_OTHER, 200 + t))) { ok = false; break; }
-                FBB_TRACE(2 + t, j, 1);
-                if (t == 0 && !all_ok(mbar_wait(v_full(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, 16 + s))) { ok = false; break; }
+            if (j + 1 < nkb) {
+                if (!all_ok(mbar_wait(s_free(t), (uint32_t)j & 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, t))) { ok = false; break; }
+                if (!all_ok(mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn))) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d = tmem_base + kColO + t * 64, pa = tmem_base + kColP + t * 64;
-                umma_ts_warp(d, pa, vd, idesc_pv, acc0);
-#pragma unroll
-                for (int k = 1; k < 8; ++k) umma_ts_warp(d, pa + 8u * k, vd + 128u * k, idesc_pv, 1u);
-                if (t == NQ - 1) umma_commit_warp(v_empty(s));
-                FBB_TRACE(2 + t, j, 2);
-                if (j + 1 < nkb) {
-                    // S_t(j+1) = Q_t . K_{j+1}^T
-                    if (t == 0 && !all_ok(mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn))) { ok = false; break; }
-                    tc_fence_after();
-                    issue_qk(t, sn);
-                    if (t == NQ - 1) umma_commit_warp(k_empty(sn));
-                    FBB_TRACE(2 + t, j, 3);
-                } else {
-                    umma_commit_warp(o_full(t));
-                }
+                issue_qk(sn);
+                FBB_TRACE(2 + t, j + 1, 3);
             }
+            if (!all_ok(mbar_wait(p_ready(t), (uint32_t)j & 1u, s_abort, DEV_TIMEOUT_OTHER, 200 + t))) { ok = false; break; }
+            if (!all_ok(mbar_wait(v_full(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, 16 + s))) { ok = false; break; }
+            tc_fence_after();
+            FBB_TRACE(2 + t, j, 1);
+            const uint64_t vd = vd0 + (uint64_t)(s * (kTileBytes >> 4));
+            umma_ts_warp(dO, aP, vd, idesc_pv, j != 0 ? 1u : 0u);
+#pragma unroll
+            for (int k = 1; k < 8; ++k) umma_ts_warp(dO, aP + 8u * k, vd + 128u * k, idesc_pv, 1u);
+            umma_commit_warp(pv_done(t));
+            umma_commit_warp(v_empty(s));
+            FBB_TRACE(2 + t, j, 2);
             s = sn;
             ph = phn;
         }
@@ -253,6 +253,9 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tmem_ld32(tS + 64, r + 64);
                 tmem_ld32(tS + 96, r + 96);
                 tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
                 if (tail) {
 #pragma unroll
                     for (int i = 0; i < 128; ++i)
@@ -273,6 +276,9 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tmem_ld32_pack16(tS, r);
                 tmem_ld32_pack16(tS + 64, r + 32);
                 tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
                 if (tail) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
@@ -290,6 +296,11 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 mx = fmaxf(__low2float(mxa), __high2float(mxa)) * sl;
             }
             if (quad == 0) FBB_TRACE(t, j, 2);
+            // O_t and P_t are still being read by P_t(j-1) . V until that product has completed (normally long ago)
+            if (j > 0) {
+                if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
+                tc_fence_after();
+            }
             // ---- running maximum: raised only when this block exceeds it by more than 2^kLazyMax
             if (j == 0) {
                 m_ref = mx;
@@ -338,7 +349,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (quad == 0) FBB_TRACE(t, j, 4);
             l_run += sum;
         }
-        if (ok && mbar_wait(o_full(t), 0, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
+        if (ok && mbar_wait(pv_done(t), (uint32_t)(nkb - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
             tc_fence_after();
             const float inv = 1.f / l_run;
             __half* dst = a.o + (int64_t)b * a.o_sb + (int64_t)row * a.o_sn + (int64_t)h * a.o_sh;
