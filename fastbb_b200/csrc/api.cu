@@ -30,7 +30,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
-                  const uint32_t* box) {
+                  const uint32_t* box, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t gdim[5];
@@ -44,7 +44,7 @@ int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* 
         if (i > 0) gstr[i - 1] = (cuuint64_t)strides_elems[i] * 2u;
     }
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return FBB_OK;

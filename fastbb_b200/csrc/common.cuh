@@ -150,6 +150,17 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* map, uint3
         : "memory");
 }
 
+// Tile store shared -> global through a tensor map (rows / columns outside the tensor are clipped by the hardware).
+__device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the bulk stores committed by this thread have finished READING shared memory (the buffer may be rewritten).
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Until the bulk stores committed by this thread have completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- tensor memory
 template <int NCOLS>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst) {  // one full warp
@@ -318,6 +329,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 // Two fp32 FMAs in one instruction (packed f32x2 pipe of sm_100): d = a * b + c element-wise.
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+#ifdef FBB_SCALAR_MATH
+    return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+#endif
     float2 d;
     asm("{\n\t"
         ".reg .b64 ra, rb, rc, rd;\n\t"
@@ -332,6 +346,9 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
     return d;
 }
 __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+#ifdef FBB_SCALAR_MATH
+    return make_float2(a.x + b.x, a.y + b.y);
+#endif
     float2 d;
     asm("{\n\t"
         ".reg .b64 ra, rb, rd;\n\t"
@@ -376,7 +393,25 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
+// Exact (erf) GELU, branch-free: x * Phi(x) with Phi from the complementary error function of |x| / sqrt(2) in the
+// rational-times-Gaussian form erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2), t = 1 / (1 + p z)
+// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7). Working from erfc keeps the negative tail accurate (no 1 - erf
+// cancellation): x > 0 -> x - x q, x <= 0 -> x q with q = erfc(z) / 2. Against float64 erf-GELU: max abs error 3.3e-7,
+// i.e. far below one fp16 rounding of the result. One reciprocal, one ex2 and nine FMAs instead of erff's two divergent
+// branches: the GELU epilogue of a 128 x 256 tile must stay shorter than the tile's main loop (K = 1024: 8.3 k clocks).
+__device__ __forceinline__ float gelu_erf(float x) {
+    const float z = fabsf(x) * 0.70710678118654752440f;
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+    const float e = ex2_approx(x * x * -0.72134752044448170368f);  // exp(-z^2)
+    float q = fmaf(1.061405429f, t, -1.453152027f);
+    q = fmaf(q, t, 1.421413741f);
+    q = fmaf(q, t, -0.284496736f);
+    q = fmaf(q, t, 0.254829592f);
+    q = 0.5f * q * t * e;
+    const float xq = x * q;
+    return x > 0.f ? x - xq : xq;
+}
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
 }  // namespace fbb

@@ -21,8 +21,7 @@
 // P.V accumulates in fp32 for every variant, because O lives in tensor memory across all key blocks: an fp16 accumulator
 // there would add N terms in fp16, where the reference's fh / hh only ever add 64 (one key block) before going to fp32.
 // The kernel is bound by the exponentials, not the tensor core: 128 x 128 of them per S tile against 16 results per
-// clock per SM from the transcendental unit is twice the time of the tile's two matrix products. A quarter of the
-// exponentials are therefore evaluated with a polynomial on the FMA pipes (exp2_emulated).
+// clock per SM from the transcendental unit is twice the time of the tile's two matrix products (1024 vs 2 x 256 clocks).
 #include "common.cuh"
 #include "internal.h"
 
@@ -33,12 +32,13 @@ constexpr int FK = 128;       // keys per block
 constexpr int kKVStages = 4;
 constexpr int kTileBytes = 128 * 64 * 2;  // one [128 x 64] fp16 tile
 constexpr float kLazyMax = 8.0f;          // raise the running maximum only beyond 2^8
-// Which of every 8 consecutive key pairs get their exponentials from the polynomial on the FMA pipes (bit i = pair i):
-// the transcendental unit (16 results per clock per SM) is what bounds this kernel, the FMA pipes have slack.
+// Which of every 8 consecutive key pairs get their exponentials from the polynomial on the FMA pipes (bit i = pair i).
+// Measured on B200 (N = 16385, 16 heads): mask 0 -> 769, 0x88 -> 781, 0xAA -> 618 TFLOP/s: the extra FMA / ALU
+// instructions cost what the transcendental unit saves, so the shipped default is 0 (the code path stays for tuning).
 #ifndef FBB_EMU_MASK
-#define FBB_EMU_MASK 0x88u
+#define FBB_EMU_MASK 0x00u
 #endif
-constexpr unsigned kEmuMask = FBB_EMU_MASK;  // 0x88: pairs 3 and 7 of 8, 25 %
+constexpr unsigned kEmuMask = FBB_EMU_MASK;  // e.g. 0x88: pairs 3 and 7 of 8 (25 %); 0: all on the transcendental unit
 // Register split of the 384-thread (NQ = 2) kernel. It is launched with 168 registers per thread (the most 12 warps can
 // get); setmaxnreg.inc WAITS until the CTA's own pool has the registers, so the split must fit in that pool or the
 // kernel never starts its softmax: 128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168.
@@ -190,6 +190,10 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         };
         bool ok = all_ok(mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100));
         if (ok) ok = all_ok(mbar_wait(k_full(0), 0, s_abort, DEV_TIMEOUT_TMA_FULL, 0));
+        // Tile 1 starts once tile 0's group has its first block in registers: the two groups then run slightly out of
+        // step, so that one group's load / maximum / store phases overlap the other group's exponentials (measured at
+        // N = 6145: 668 -> 695 TFLOP/s for ff, 600 -> 667 for hh; longer offsets change nothing).
+        if (ok && t == 1 && nkb > 2) ok = all_ok(mbar_wait(s_free(0), 0, s_abort, DEV_TIMEOUT_TMEM_EMPTY, 50));
         if (ok) {
             tc_fence_after();
             issue_qk(0);

@@ -5,7 +5,7 @@
 // Persistent kernel, one CTA per SM, 128 x BN output tiles, K consumed in 64-element (128-byte) blocks:
 //   warp 0      TMA producer: A box [64 x 128] and W box [64 x BN] per stage (128-byte swizzle, zero fill outside)
 //   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage into one of two tensor-memory accumulators
-//   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> 16-byte stores
+//   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> shared staging tile -> TMA store
 // The two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
 // Both operands are K-major, so neither is transposed: nn.Linear's [N, K] weight is exactly the B operand.
 #include "common.cuh"
@@ -25,7 +25,9 @@ struct GemmSmem {
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kParamFloats = 2 * 2 * BN;  // double-buffered bias + gamma
-    static constexpr int kBarOffset = kStages * kStageBytes + kParamFloats * 4;
+    static constexpr int kStoreBytes = 8 * 32 * 32 * 2;  // one [32 rows x 32 columns] fp16 staging tile per epilogue warp
+    static constexpr int kStoreOffset = kStages * kStageBytes + kParamFloats * 4;
+    static constexpr int kBarOffset = kStoreOffset + kStoreBytes;
     static constexpr int kNumBars = 2 * kStages + 4;
     static constexpr int kBytes = kBarOffset + kNumBars * 8 + 16;
     static constexpr int kDynamic = kBytes + 1024;  // slack to align the tile base to 1024 bytes
@@ -46,7 +48,8 @@ struct GemmArgs {
 
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmArgs g) {
+linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
     using S = GemmSmem<BN>;
     constexpr int kStages = S::kStages;
     constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
@@ -81,6 +84,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
         __syncwarp();
@@ -157,6 +161,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const int quad = warp & 3;        // tensor-memory lane quadrant this warp may read
         const int chalf = ew >> 2;        // which half of the output columns
         const int et = threadIdx.x - 64;  // 0..255
+        uint8_t* stage_gen = gen + S::kStoreOffset + ew * 2048;
+        const uint32_t stage_addr = base + S::kStoreOffset + ew * 2048;
         int acc = 0;
         uint32_t acc_ph = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -180,7 +186,6 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const int row = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             const bool row_ok = row < g.M;
-            __half* c_row = g.C + (int64_t)row * g.ldc;
             const __half* r_row = g.res != nullptr ? g.res + (int64_t)row * g.ldr : nullptr;
 #pragma unroll 1
             for (int c0 = chalf * (kOutCols / 2); c0 < (chalf + 1) * (kOutCols / 2); c0 += 32) {
@@ -213,29 +218,42 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
                     }
                 }
-                if (row_ok) {
+                // residual + LayerScale on the columns that exist (n_out % 8 == 0: a group of 8 is all in or all out)
+                if (!SWIGLU && r_row != nullptr && row_ok) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int col = n0 + c0 + q * 8;
-                        if (col < g.n_out) {  // n_out % 8 == 0: a group of 8 is all in or all out
-                            if (!SWIGLU && r_row != nullptr) {
-                                const uint4 rv = *reinterpret_cast<const uint4*>(r_row + col);
-                                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+                        if (col < g.n_out) {
+                            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + col);
+                            const __half2* rh = reinterpret_cast<const __half2*>(&rv);
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float2 rf = __half22float2(rh[j]);
-                                    v[q * 8 + 2 * j] = fmaf(s_gamma[c0 + q * 8 + 2 * j], v[q * 8 + 2 * j], rf.x);
-                                    v[q * 8 + 2 * j + 1] = fmaf(s_gamma[c0 + q * 8 + 2 * j + 1], v[q * 8 + 2 * j + 1], rf.y);
-                                }
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 rf = __half22float2(rh[j]);
+                                v[q * 8 + 2 * j] = fmaf(s_gamma[c0 + q * 8 + 2 * j], v[q * 8 + 2 * j], rf.x);
+                                v[q * 8 + 2 * j + 1] = fmaf(s_gamma[c0 + q * 8 + 2 * j + 1], v[q * 8 + 2 * j + 1], rf.y);
                             }
-                            uint4 o;
-                            o.x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
-                            o.y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
-                            o.z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
-                            o.w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
-                            *reinterpret_cast<uint4*>(c_row + col) = o;
                         }
                     }
+                }
+                // fp16 -> this warp's staging tile (64-byte rows, 16-byte chunks XOR-swizzled as the tensor map's 64-byte
+                // mode expects: conflict-free) -> one TMA store of [32 rows x 32 columns]; rows >= M and columns >= n_out
+                // are clipped by the hardware. The previous store must have finished reading the tile first.
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
+                    o.y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
+                    o.z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
+                    o.w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
+                    *reinterpret_cast<uint4*>(stage_gen + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && n0 + c0 < g.n_out && m0 + quad * 32 < g.M) {
+                    tma_store_2d(&tmap_c, stage_addr, n0 + c0, m0 + quad * 32);
+                    bulk_commit();
                 }
             }
             tc_fence_before();
@@ -243,6 +261,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
         }
+        if (lane == 0) bulk_wait_all();  // this warp's output stores are complete before the CTA gives up its shared memory
     }
 
     tc_fence_before();
@@ -255,7 +274,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 }
 
 template <int BN, bool SWIGLU>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, GemmArgs g, cudaStream_t stream) {
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmArgs g, cudaStream_t stream) {
     using S = GemmSmem<BN>;
     static bool configured[64] = {};
     int dev = 0;
@@ -271,7 +290,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, GemmArgs
     g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
     const int tiles = g.tiles_m * g.tiles_n;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    kern<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tw, g);
+    kern<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tw, tc, g);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
@@ -317,9 +336,16 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     st = make_tmap_f16(&tw, W, 2, dims_w, str_w, box_w);
     if (st != FBB_OK) return st;
 
-    if (swiglu) return launch_variant<256, true>(ta, tw, g, stream);
-    if (use128) return launch_variant<128, false>(ta, tw, g, stream);
-    return launch_variant<256, false>(ta, tw, g, stream);
+    CUtensorMap tc;
+    uint64_t dims_c[2] = {(uint64_t)g.n_out, (uint64_t)M};
+    int64_t str_c[2] = {1, ldc};
+    uint32_t box_c[2] = {32, 32};
+    st = make_tmap_f16(&tc, C, 2, dims_c, str_c, box_c, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (st != FBB_OK) return st;
+
+    if (swiglu) return launch_variant<256, true>(ta, tw, tc, g, stream);
+    if (use128) return launch_variant<128, false>(ta, tw, tc, g, stream);
+    return launch_variant<256, false>(ta, tw, tc, g, stream);
 }
 
 }  // namespace fbb

@@ -20,9 +20,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn encode_tiled_fn();
 
 // fp16 tensor map with 128-byte swizzle, zero fill outside the tensor. dims/strides innermost first; strides in
-// elements for dims 1..rank-1 (dim 0 is contiguous); box innermost first (box[0] must be 64 elements = 128 bytes).
+// elements for dims 1..rank-1 (dim 0 is contiguous); box innermost first (box[0] * 2 bytes = the swizzle span: 64
+// elements for the 128-byte mode, 32 for the 64-byte mode).
 int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
-                  const uint32_t* box);
+                  const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 int num_sms();  // SM count of the current device
 
