@@ -1,6 +1,7 @@
 // The extern "C" surface of libfastbb_b200.so: argument validation on the host, then one launch per call.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -61,6 +62,14 @@ int num_sms() {
         cached[dev] = n > 0 ? n : 148;
     }
     return cached[dev];
+}
+
+bool pdl_enabled() {
+    static const bool on = []() {
+        const char* e = getenv("FBB_NO_PDL");
+        return !(e != nullptr && e[0] == '1');
+    }();
+    return on;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

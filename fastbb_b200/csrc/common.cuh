@@ -58,6 +58,12 @@ __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.
 template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while the
+// previous kernel of the stream is still draining; everything before this wait (barrier set-up, tensor-memory
+// allocation, descriptor prefetch) overlaps that tail, everything after it sees the previous kernel's memory.
+// Without the attribute the instruction does nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -139,6 +139,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
 
     // Warpgroup 0 holds the two single-thread roles (and two idle warps) and gives registers away; the softmax
     // warpgroups take them: a softmax thread keeps a whole 128-key row of S in registers.
@@ -238,11 +239,26 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const float sl = a.scale_log2;
         float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
+        // A warp whose 32 rows all lie beyond N (the padding of the last tile) only keeps the barriers moving: the
+        // rows of P, S and O it would touch feed nothing that is stored.
+        const bool warp_has_rows = q0 + t * FQ + quad * 32 < a.N;
 
         for (int j = 0; j < nkb; ++j) {
             if (quad == 0) FBB_TRACE(t, j, 0);
             if (!mbar_wait(s_full(t), j & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, t)) { ok = false; break; }
             tc_fence_after();
+            if (!warp_has_rows) {
+                // S_t(j+1) can be ready long before the other warps have written P_t(j): this warp's arrival for block
+                // j must not land in the phase of block j-1, so it watches that phase complete first.
+                if (j > 0 && !mbar_wait(p_ready(t), (uint32_t)(j - 1) & 1u, s_abort, DEV_TIMEOUT_OTHER, 210 + t)) { ok = false; break; }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(s_free(t));
+                    mbar_arrive(p_ready(t));
+                }
+                continue;
+            }
             if (quad == 0) FBB_TRACE(t, j, 1);
             const int key0 = j * FK;
             const bool tail = key0 + FK > a.N;
@@ -353,7 +369,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (quad == 0) FBB_TRACE(t, j, 4);
             l_run += sum;
         }
-        if (ok && mbar_wait(pv_done(t), (uint32_t)(nkb - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
+        if (ok && warp_has_rows && mbar_wait(pv_done(t), (uint32_t)(nkb - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
             tc_fence_after();
             const float inv = 1.f / l_run;
             __half* dst = a.o + (int64_t)b * a.o_sb + (int64_t)row * a.o_sn + (int64_t)h * a.o_sh;
@@ -399,8 +415,7 @@ static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, co
         configured[dev] = true;
     }
     dim3 grid((unsigned)((a.N + FQ * NQ - 1) / (FQ * NQ)), (unsigned)(B * a.H), 1);
-    kern<<<grid, 128 + 128 * NQ, FlashSmem::kDynamic, stream>>>(tq, tk, tv, a);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(kern, grid, dim3(128 + 128 * NQ), FlashSmem::kDynamic, stream, tq, tk, tv, a);
     if (e != cudaSuccess) return fail((int)e, "flash64_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }

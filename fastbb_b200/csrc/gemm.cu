@@ -95,6 +95,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -290,8 +291,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
     const int tiles = g.tiles_m * g.tiles_n;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    kern<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tw, tc, g);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, ta, tw, tc, g);
     if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }

@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const void* __restr
                                                             int in_dtype, int param_dtype) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_dependency_wait();
     if (row >= M) return;
     const int nvec = C >> 3;
     float v[NV][8];
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(256) layernorm_long_rows_kernel(const void* __
                                                                  int in_dtype, int param_dtype) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_dependency_wait();
     if (row >= M) return;
     const int nvec = C >> 3;
     float f[8];
@@ -150,9 +152,10 @@ int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64
     const unsigned grid = (unsigned)((M + warps - 1) / warps);
     const int nv = (C / 8 + 31) / 32;
     __half* yh = reinterpret_cast<__half*>(y);
+    cudaError_t err = cudaSuccess;
 #define FBB_LN_CASE(N)                                                                                              \
     case N:                                                                                                         \
-        layernorm_rows_kernel<N><<<grid, warps * 32, 0, stream>>>(x, yh, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype); \
+        err = launch_pdl(layernorm_rows_kernel<N>, dim3(grid), dim3(warps * 32), 0, stream, x, yh, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype); \
         break;
     switch (nv) {
         FBB_LN_CASE(1)
@@ -164,10 +167,10 @@ int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64
         FBB_LN_CASE(7)
         FBB_LN_CASE(8)
         default:
-            layernorm_long_rows_kernel<<<grid, warps * 32, 0, stream>>>(x, yh, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype);
+            err = launch_pdl(layernorm_long_rows_kernel, dim3(grid), dim3(warps * 32), 0, stream, x, yh, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype);
     }
 #undef FBB_LN_CASE
-    return cuda_status(cudaGetLastError());
+    return cuda_status(err);
 }
 
 }  // namespace fbb

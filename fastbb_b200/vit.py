@@ -119,6 +119,7 @@ class FastViT:
         self.graphs, self.graph_noclone = graphs, graph_noclone
         self._graphs, self._pool, self._graph_version = {}, None, None
         self._orig = {}
+        self._patch_w, self._patch_w_version = None, None
 
     _version = staticmethod(_param_version)
 
@@ -159,16 +160,57 @@ class FastViT:
             table = self._pos[(h0, w0)] = table.to(self.dtype)
         return table
 
+    def _patch_gemm_weight(self):
+        """[C, 4*ps*ps] fp16 view of a plain patch-embedding convolution (kernel = stride = patch, 3 input channels, no norm)
+        with a zero fourth input channel, so that the reduction length is a multiple of 8; None when the model's patch
+        embedding is anything else (then its own forward is used). Cached until the weight is reloaded."""
+        pe = getattr(self.vit, "patch_embed", None)
+        proj = getattr(pe, "proj", None)
+        ps = self.ps
+        plain = (isinstance(proj, torch.nn.Conv2d) and proj.kernel_size == (ps, ps) and proj.stride == (ps, ps)
+                 and proj.padding == (0, 0) and proj.dilation == (1, 1) and proj.groups == 1 and proj.in_channels == 3
+                 and _ident(getattr(pe, "norm", None)) and (4 * ps * ps) % 8 == 0 and proj.weight.is_cuda
+                 and proj.weight.dtype == self.dtype and getattr(pe, "flatten", True) is not False)
+        if not plain:
+            return None, None
+        version = _param_version((proj.weight,))
+        if version is None or version != self._patch_w_version:
+            w = proj.weight.detach()
+            w4 = torch.zeros(w.shape[0], 4, ps, ps, dtype=w.dtype, device=w.device)
+            w4[:, :3] = w
+            self._patch_w, self._patch_w_version = w4.reshape(w.shape[0], 4 * ps * ps), version
+        return self._patch_w, proj.bias
+
     def tokens(self, x):
-        """Image batch [B, 3, H, W] -> tokens [B, 1 + nreg + hw, C]: the model's own patch embedding, cls token,
-        position table, registers after cls. Stays PyTorch host code (0.1 % of the FLOPs at 896x1344)."""
+        """Image batch [B, 3, H, W] -> tokens [B, 1 + nreg + hw, C] (fastbb/vit.py:97-105): patch embedding, cls token,
+        position table, registers after cls. A plain patch-embedding convolution runs as one GEMM per image on the
+        linear kernel, with the bias and the position table fused into its epilogue and the result written straight
+        into the token buffer; any other patch-embedding module runs as the model's own code."""
         vit = self.vit
         B, _, h, w = x.shape
-        t = vit.patch_embed(x.to(self.dtype))
-        t = torch.cat([vit.cls_token.to(self.dtype).expand(B, -1, -1), t], 1)
-        t = t + self.pos_embed(h // self.ps, w // self.ps)
-        if self.nreg:
-            t = torch.cat([t[:, :1], vit.register_tokens.to(self.dtype).expand(B, -1, -1), t[:, 1:]], 1)
+        h0, w0 = h // self.ps, w // self.ps
+        pos = self.pos_embed(h0, w0)
+        w4, bias = self._patch_gemm_weight() if (x.is_cuda and h % self.ps == 0 and w % self.ps == 0) else (None, None)
+        if w4 is None:
+            t = vit.patch_embed(x.to(self.dtype))
+            t = torch.cat([vit.cls_token.to(self.dtype).expand(B, -1, -1), t], 1)
+            t = t + pos
+            if self.nreg:
+                t = torch.cat([t[:, :1], vit.register_tokens.to(self.dtype).expand(B, -1, -1), t[:, 1:]], 1)
+            return t
+        ps, C, nreg = self.ps, w4.shape[0], self.nreg
+        # unfold into [B, h0*w0, 4*ps*ps] (one strided copy that also casts to fp16; the fourth channel is zero)
+        patches = torch.empty(B, h0, w0, 4, ps, ps, dtype=self.dtype, device=x.device)
+        patches[:, :, :, :3].copy_(x.reshape(B, 3, h0, ps, w0, ps).permute(0, 2, 4, 1, 3, 5))
+        patches[:, :, :, 3].zero_()
+        patches = patches.view(B, h0 * w0, 4 * ps * ps)
+        t = torch.empty(B, 1 + nreg + h0 * w0, C, dtype=self.dtype, device=x.device)
+        t[:, 0] = vit.cls_token.to(self.dtype)[0, 0] + pos[0, 0]
+        if nreg:
+            t[:, 1:1 + nreg] = vit.register_tokens.to(self.dtype)
+        pos_patches = pos[0, 1:]
+        for b in range(B):
+            linear(patches[b], w4, bias, res=pos_patches, variant="f32", out=t[b, 1 + nreg:])
         return t
 
     # ------------------------------------------------------------------ block
