@@ -9,7 +9,9 @@ independent replica on its own GPU (weak scaling, no collective on the forward p
 reduced (MAX over ranks). Prints ONE JSON line on rank 0.
 
   value     images/s with the input image already resident in HBM (CUDA events around exactly K steps)
-  e2e       the same through the public API from a pinned host image to pinned host outputs, copies inside the timing
+  e2e       the same through the public API (fastbb_b200.pipeline.HostPipeline) from a pinned host image to pinned host
+            outputs: every step uploads its image and downloads its features inside the timed region, on copy streams
+            overlapped with compute
   roofline  the dominant kernel (flash attention): algorithmic FLOPs per launch / mean launch time, timed live with
             CUDA events around each of its launches in a separate instrumented pass over the same K steps
   cpu_baseline / --impl reference
@@ -149,10 +151,6 @@ def run_ours(args, rank, local_rank, world):
     outs = step(x_dev)
     launches_per_step = _lib.LAUNCHES - before
     fast.graphs = graphs
-    host_out = [(torch.empty(p.shape, dtype=p.dtype).pin_memory(), torch.empty(c.shape, dtype=c.dtype).pin_memory()) for p, c in outs]
-    d2h = sum(p.numel() * p.element_size() + c.numel() * c.element_size() for p, c in outs)
-    h2d = x_host.numel() * x_host.element_size()
-
     for _ in range(max(args.warmup, 3)):
         step(x_dev)
     torch.cuda.synchronize()
@@ -173,24 +171,27 @@ def run_ours(args, rank, local_rank, world):
     ms_total = replicas.max_over_ranks(e0.elapsed_time(e1), dev)
     clocks = sampler.summary()
 
-    # ---------------- end to end: pinned host image in, pinned host features out, copies inside the timing
-    def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        res = step(xd)
-        for (p, c), (hp, hc) in zip(res, host_out):
-            hp.copy_(p, non_blocking=True)
-            hc.copy_(c, non_blocking=True)
-    for _ in range(2):
-        e2e_step()
+    # ---------------- end to end: pinned host image in, pinned host features out, every step's copies inside the timing.
+    # Through the package's HostPipeline: uploads and downloads run on side streams, overlapped with the next / previous
+    # step's compute (each step still uploads its own image and downloads its own features).
+    from fastbb_b200.pipeline import HostPipeline
+    pipe = HostPipeline(step, device=dev, depth=2)
+    for _ in range(3):
+        pipe.submit(x_host)
+    pipe.drain()
     torch.cuda.synchronize()
     replicas.barrier()
     e0.record()
     for _ in range(args.steps):
-        e2e_step()
+        pipe.submit(x_host)
+    pipe.drain()
     e1.record()
     torch.cuda.synchronize()
     replicas.barrier()
     ms_e2e = replicas.max_over_ranks(e0.elapsed_time(e1), dev)
+    host_check = pipe.result(pipe.drain())
+    assert all(torch.isfinite(p.float()).all() for p, _ in host_check), "non-finite features in the end-to-end pass"
+    h2d, d2h = pipe.h2d_bytes, pipe.d2h_bytes
 
     # ---------------- roofline of the dominant kernel: events around every flash-attention launch, eager pass
     variant = "ff" if fast.attn == "sdpa" else fast.attn

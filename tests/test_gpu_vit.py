@@ -182,3 +182,28 @@ def test_c2_timm_like_block_stack(oracle, spec, batch):
     for bi in range(batch):
         assert oracle.rel_l2(y[bi:bi + 1, ::int(g["token_stride"])].cpu(), torch.from_numpy(g["out"])) < TOL[spec]
     assert abs(float(y[0].double().norm()) / float(g["out_norm"]) - 1) < TOL[spec]
+
+
+def test_host_pipeline_matches_direct_calls(oracle):
+    """Uploads / downloads on side streams must not change results, also when buffers are reused across submissions."""
+    from fastbb_b200.models.dinov2 import dinov2
+    from fastbb_b200.pipeline import HostPipeline
+    params = oracle.make_params("vits14", seed=0, depth=3)
+    fast = dinov2("vits14", params, spec="fh-g0-graph", device="cuda:0")
+    fn = lambda x: fast.get_intermediate_layers(x, n=[0, 2], return_class_token=True)  # noqa: E731
+    imgs = [oracle.make_image(2, 224, 224, seed=20 + i).pin_memory() for i in range(5)]
+    pipe = HostPipeline(fn, device="cuda:0", depth=2)
+    got = []
+    tickets = []
+    for i, img in enumerate(imgs):
+        tickets.append(pipe.submit(img))
+        if i >= 1:  # collect one behind, as a serving loop would
+            got.append([(p.clone(), c.clone()) for p, c in pipe.result(tickets[i - 1])])
+    got.append([(p.clone(), c.clone()) for p, c in pipe.result(tickets[-1])])
+    for img, res in zip(imgs, got):
+        want = fn(img.to("cuda:0"))
+        for (p, c), (wp, wc) in zip(res, want):
+            assert torch.equal(p, wp.cpu()) and torch.equal(c, wc.cpu())
+    assert pipe.h2d_bytes == 2 * 3 * 224 * 224 * 4 and pipe.d2h_bytes == 2 * 2 * (256 + 1) * 384 * 2
+    with pytest.raises(ValueError):
+        pipe.result(tickets[0])
