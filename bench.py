@@ -87,6 +87,10 @@ def oracle_cpu_sample(steps, warmup, blocks=3):
     896x1344 image per step; the block time is scaled to 24 blocks (all blocks cost the same). Returns (img/s, info)."""
     import torch
     from oracle import vit_oracle as O
+    try:  # torchrun exports OMP_NUM_THREADS=1; the CPU baseline uses every core this process may run on
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     params = O.make_params(ARCH, seed=0, depth=blocks)
     x = O.make_image(1, IMG_H, IMG_W, seed=1)
     times = []
