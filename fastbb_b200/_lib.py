@@ -28,6 +28,7 @@ PROTOTYPES = {
     "fbb_status_string": (ctypes.c_char_p, [_i32]),
     "fbb_last_error": (ctypes.c_char_p, []),
     "fbb_device_status": (_i32, [ctypes.POINTER(ctypes.c_uint * 4)]),
+    "fbb_linear_max_cta_pairs": (_i32, [_i32]),
     "fbb_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _f32, _i32, _i32, _vp]),
     "fbb_linear_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),

@@ -112,6 +112,11 @@ int fbb_device_status(unsigned int out[4]) {
     return FBB_OK;
 }
 
+int fbb_linear_max_cta_pairs(int tile_columns) {
+    if (tile_columns != 128 && tile_columns != 256) return fail(FBB_ERR_ENUM, "tile_columns must be 128 or 256");
+    return linear_max_pairs(tile_columns);
+}
+
 int fbb_layernorm_f16(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
                       float eps, int in_dtype, int param_dtype, void* stream) {
     if (x == nullptr || y == nullptr) return fail(FBB_ERR_NULL, "layernorm: x or y is null");

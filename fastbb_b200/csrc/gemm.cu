@@ -2,13 +2,18 @@
 // Replaces F.linear + the separate bias / GELU / SwiGLU / LayerScale-residual passes of fastbb/vit.py:114-143 and the
 // gemm_tn_* kernels of fastbb/fastbb_kernels.cu:323-446 (epilogue order bias -> act -> res + gamma*v, :418-427).
 //
-// Persistent kernel, one CTA per SM, 128 x BN output tiles, K consumed in 64-element (128-byte) blocks:
+// Persistent kernel, one CTA per SM, 128 x BN output tiles per CTA, K consumed in 64-element (128-byte) blocks. Two forms:
+// one CTA per tile (cta_group::1), or a pair of CTAs (cluster of two, cta_group::2) on a 256 x BN tile, where each CTA
+// stages its 128 rows of A and BN/2 of the W rows and the leader CTA issues UMMAs that read both CTAs' shared memory
+// (no multicast load: each CTA fetches its own operands; only barrier signals cross the pair).
 //   warp 0      TMA producer: A box [64 x 128] and W box [64 x BN] per stage (128-byte swizzle, zero fill outside)
 //   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage into one of two tensor-memory accumulators
 //   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> shared staging tile -> TMA store
 // The two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
 // Both operands are K-major, so neither is transposed: nn.Linear's [N, K] weight is exactly the B operand.
 #include "common.cuh"
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace fbb {
@@ -18,11 +23,13 @@ constexpr int BK = 64;
 constexpr int kGemmThreads = 320;
 constexpr int kEpiThreads = 256;
 
-template <int BN>
+// CTA2: the CTA is one half of a pair (cta_group::2) that computes a 256-row tile; it stages its 128 rows of A and only
+// BN/2 of the BN rows of W per k-block, which is what brings the operand traffic per FLOP down.
+template <int BN, bool CTA2>
 struct GemmSmem {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
     static constexpr int kABytes = BM * BK * 2;
-    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kBBytes = (CTA2 ? BN / 2 : BN) * BK * 2;
+    static constexpr int kStages = (kABytes + kBBytes) == 49152 ? 4 : ((kABytes + kBBytes) == 32768 ? 6 : 8);
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kParamFloats = 2 * 2 * BN;  // double-buffered bias + gamma
     static constexpr int kStoreBytes = 8 * 32 * 32 * 2;  // one [32 rows x 32 columns] fp16 staging tile per epilogue warp
@@ -46,11 +53,16 @@ struct GemmArgs {
     int tiles_m, tiles_n;
 };
 
-template <int BN, bool SWIGLU>
+template <int BN, bool SWIGLU, bool CTA2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
-    using S = GemmSmem<BN>;
+    using S = GemmSmem<BN, CTA2>;
+    // pair geometry: rank 0 (the leader) issues the UMMAs; work items are 256-row tiles shared by the pair
+    const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;
+    const int worker = CTA2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int num_workers = CTA2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int kTileRows = CTA2 ? 2 * BM : BM;
     constexpr int kStages = S::kStages;
     constexpr int kOutCols = SWIGLU ? BN / 2 : BN;  // output columns per tile
     extern __shared__ uint8_t smem_raw[];
@@ -78,7 +90,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kEpiThreads / 32);
+            mbar_init(tempty_bar(a), (CTA2 ? 2 : 1) * kEpiThreads / 32);  // the leader's barrier also counts the peer's warps
         }
         *s_abort = 0;
         fence_barrier_init();
@@ -88,11 +100,17 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
     if (warp == 1) {
         __syncwarp();
-        tmem_alloc<2 * BN>(smem_u32(const_cast<uint32_t*>(s_tmem)));
-        tmem_relinquish();
+        if constexpr (CTA2) {
+            tmem_alloc_pair<2 * BN>(smem_u32(const_cast<uint32_t*>(s_tmem)));
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc<2 * BN>(smem_u32(const_cast<uint32_t*>(s_tmem)));
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (CTA2) cluster_sync_all();  // both CTAs' barriers exist before either signals the other
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
@@ -103,32 +121,41 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / g.tiles_n) * BM;
+            for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+                const int m0 = (tile / g.tiles_n) * kTileRows + (int)rank * BM;
                 const int nt = tile % g.tiles_n;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
                     const uint32_t sa = base + s * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
-                    mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-                    tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, m0);
-                    if (SWIGLU) {
-                        // x1 rows [nt*BN/2, +BN/2) and the matching x2 rows, offset by N/2
-                        tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * (BN / 2));
-                        tma_load_2d(sb + S::kBBytes / 2, &tmap_w, full_bar(s), kb * BK, g.N / 2 + nt * (BN / 2));
+                    if constexpr (CTA2) {
+                        // the leader's barrier collects the bytes of both CTAs; each CTA loads its own A rows and its half of
+                        // the W rows (SwiGLU: the leader the x1 rows, the peer the matching x2 rows)
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
+                        tma_load_2d_pair(sa, &tmap_a, full_bar(s), kb * BK, m0);
+                        const int wrow = SWIGLU ? (rank == 0 ? nt * (BN / 2) : g.N / 2 + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2);
+                        tma_load_2d_pair(sb, &tmap_w, full_bar(s), kb * BK, wrow);
                     } else {
-                        tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * BN);
+                        mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+                        tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, m0);
+                        if (SWIGLU) {
+                            // x1 rows [nt*BN/2, +BN/2) and the matching x2 rows, offset by N/2
+                            tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * (BN / 2));
+                            tma_load_2d(sb + S::kBBytes / 2, &tmap_w, full_bar(s), kb * BK, g.N / 2 + nt * (BN / 2));
+                        } else {
+                            tma_load_2d(sb, &tmap_w, full_bar(s), kb * BK, nt * BN);
+                        }
                     }
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
             if (!ok) __nanosleep(20000);  // let copies already in flight land before the CTA leaves
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ UMMA issuer
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------------------------ UMMA issuer (the leader CTA of a pair only)
         // The whole warp runs this loop and one elected lane issues each instruction, so that descriptors and
         // addresses are warp-uniform values (uniform registers) rather than per-thread arithmetic in a divergent branch.
-        const uint32_t idesc = make_idesc_f16(BM, BN, !g.acc_f16, false, false);
+        const uint32_t idesc = make_idesc_f16(kTileRows, BN, !g.acc_f16, false, false);
         constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
         const uint64_t adesc0 = smem_desc(base, desc_hi);
         auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
@@ -137,7 +164,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
             if (!all_ok(mbar_wait(tempty_bar(acc), acc_ph ^ 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, acc))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -146,17 +173,25 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 tc_fence_after();
                 const uint64_t adesc = adesc0 + (uint64_t)(s * (S::kStageBytes >> 4));
                 const uint64_t bdesc = adesc + (uint64_t)(S::kABytes >> 4);
-                umma_ss_warp(d_tmem, adesc, bdesc, idesc, kb != 0 ? 1u : 0u);
+                if constexpr (CTA2) {
+                    umma_ss_pair_warp(d_tmem, adesc, bdesc, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 1; k < BK / 16; ++k) umma_ss_warp(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, 1u);
-                umma_commit_warp(empty_bar(s));  // stage reusable once these UMMAs have read it
+                    for (int k = 1; k < BK / 16; ++k) umma_ss_pair_warp(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, 1u);
+                    umma_commit_pair_warp(empty_bar(s));  // frees the stage in both CTAs
+                } else {
+                    umma_ss_warp(d_tmem, adesc, bdesc, idesc, kb != 0 ? 1u : 0u);
+#pragma unroll
+                    for (int k = 1; k < BK / 16; ++k) umma_ss_warp(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, 1u);
+                    umma_commit_warp(empty_bar(s));  // stage reusable once these UMMAs have read it
+                }
                 if (++s == kStages) { s = 0; ph ^= 1u; }
             }
             if (!ok) break;
-            umma_commit_warp(tfull_bar(acc));  // accumulator complete
+            if constexpr (CTA2) umma_commit_pair_warp(tfull_bar(acc));  // both CTAs' accumulators complete
+            else umma_commit_warp(tfull_bar(acc));
             if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
         }
-    } else {
+    } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue (8 warps)
         const int ew = warp - 2;
         const int quad = warp & 3;        // tensor-memory lane quadrant this warp may read
@@ -166,8 +201,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const uint32_t stage_addr = base + S::kStoreOffset + ew * 2048;
         int acc = 0;
         uint32_t acc_ph = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int m0 = (tile / g.tiles_n) * BM;
+        for (int tile = worker; tile < num_tiles; tile += num_workers) {
+            const int m0 = (tile / g.tiles_n) * kTileRows + (int)rank * BM;
             const int nt = tile % g.tiles_n;
             const int n0 = nt * kOutCols;  // first output column of the tile
             // stage bias (W-row indexed) and gamma (output-column indexed) for this tile
@@ -259,7 +294,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (lane == 0) {
+                if constexpr (CTA2) mbar_arrive_remote(tempty_bar(acc), 0u);  // the leader issues the next tile for both CTAs
+                else mbar_arrive(tempty_bar(acc));
+            }
             if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
         }
         if (lane == 0) bulk_wait_all();  // this warp's output stores are complete before the CTA gives up its shared memory
@@ -267,34 +305,80 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
     tc_fence_before();
     __syncthreads();
+    if constexpr (CTA2) cluster_sync_all();  // the peer may still be signalling this CTA's barriers / reading its operands
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc<2 * BN>(tmem_base);
+        if constexpr (CTA2) tmem_dealloc_pair<2 * BN>(tmem_base);
+        else tmem_dealloc<2 * BN>(tmem_base);
     }
 }
 
+// Clusters of two that can be resident at once for this kernel on the current device (0: pairs cannot be launched).
 template <int BN, bool SWIGLU>
+static int max_pairs() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        using S = GemmSmem<BN, true>;
+        auto kern = linear_umma_kernel<BN, SWIGLU, true>;
+        int n = 0;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * num_sms());
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = S::kDynamic;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+            cudaGetLastError();
+        }
+        cached[dev] = n > 0 ? n : -1;
+    }
+    return cached[dev] > 0 ? cached[dev] : 0;
+}
+
+template <int BN, bool SWIGLU, bool CTA2>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmArgs g, cudaStream_t stream) {
-    using S = GemmSmem<BN>;
+    using S = GemmSmem<BN, CTA2>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = linear_umma_kernel<BN, SWIGLU>;
+    auto kern = linear_umma_kernel<BN, SWIGLU, CTA2>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(linear_umma_kernel): %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
     constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
-    g.tiles_m = (g.M + BM - 1) / BM;
+    constexpr int kTileRows = CTA2 ? 2 * BM : BM;
+    g.tiles_m = (g.M + kTileRows - 1) / kTileRows;
     g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
     const int tiles = g.tiles_m * g.tiles_n;
-    const int grid = tiles < num_sms() ? tiles : num_sms();
-    cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, ta, tw, tc, g);
+    const int workers_max = CTA2 ? max_pairs<BN, SWIGLU>() : num_sms();
+    const int workers = tiles < workers_max ? tiles : workers_max;
+    const int grid = CTA2 ? 2 * workers : workers;
+    cudaError_t e = launch_pdl_cluster(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, CTA2 ? 2u : 1u, ta, tw, tc, g);
     if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }
+
+static bool gemm_pairs_enabled() {
+    static const bool on = []() {
+        const char* e = getenv("FBB_GEMM_1CTA");
+        return !(e != nullptr && e[0] == '1');
+    }();
+    return on;
+}
+
+int linear_max_pairs(int bn) { return bn == 128 ? max_pairs<128, false>() : max_pairs<256, false>(); }
 
 int launch_linear(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
@@ -316,13 +400,36 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     g.acc_f16 = accumulate == FBB_ACC_F16 ? 1 : 0;
     g.tiles_m = g.tiles_n = 0;
 
-    // Tile width: 256 columns unless 128-column tiles fill the SMs with clearly fewer idle slots in the last wave.
+    // Shape of the work item: one CTA with a 128x256 or 128x128 tile, or a CTA pair with a 256x256 tile (each CTA stages
+    // its 128 rows of A and half of the W rows, which cuts the operand traffic from L2 per FLOP by a third).
+    // Picked by a small cost model in units of one 128x256 one-CTA tile: waves of tiles over the workers (148 CTAs or 74
+    // pairs) times the relative tile time, fitted to measurements on B200: 128-column tiles 0.60 (they move 1.3x the
+    // operand bytes per FLOP), a pair's tile 0.895 per CTA plus a start-up term for the cluster launch that matters when
+    // the per-tile K loop is short (M = 32768, N = 4096, K = 1024: 219 us one-CTA, 196 us pairs; M = 6145: 48 vs 50 us).
+    // Pairs with 128-column tiles measured no better than single CTAs and are only reachable through the override.
+    // FBB_GEMM_FORCE = s256 | s128 | p256 | p128 overrides the choice (tuning aid).
     const int sms = num_sms();
-    const int64_t tm = (M + BM - 1) / BM;
-    const int64_t t256 = tm * ((g.n_out + 255) / 256), t128 = tm * ((g.n_out + 127) / 128);
-    const double cost256 = (double)((t256 + sms - 1) / sms) * 2.0;
-    const double cost128 = (double)((t128 + sms - 1) / sms) * 1.15;
-    const bool use128 = !swiglu && (g.n_out <= 128 || cost128 < cost256);
+    const bool pairs_ok = gemm_pairs_enabled();
+    const int pairs256 = pairs_ok ? (swiglu ? max_pairs<256, true>() : max_pairs<256, false>()) : 0;
+    auto waves = [](int64_t tiles, int workers) { return (double)((tiles + workers - 1) / workers); };
+    const int64_t tm1 = (M + BM - 1) / BM, tm2 = (M + 2 * BM - 1) / (2 * BM);
+    const int64_t tn256 = (g.n_out + 255) / 256, tn128 = (g.n_out + 127) / 128;
+    double best = waves(tm1 * tn256, sms) * 1.0;
+    bool use_pairs = false, use128 = false;
+    if (!swiglu) {
+        const double c = waves(tm1 * tn128, sms) * 0.60;
+        if (g.n_out <= 128 || c < best) { best = c; use128 = true; }
+    }
+    if (pairs256 > 0) {
+        const double c = waves(tm2 * tn256, pairs256) * 0.895 + (K < 1536 ? 0.7 : 0.2);
+        if (c < best) { best = c; use_pairs = true; use128 = false; }
+    }
+    if (const char* f = getenv("FBB_GEMM_FORCE")) {
+        if (!swiglu && (f[0] == 's' || (f[0] == 'p' && pairs256 > 0 && max_pairs<128, false>() > 0))) {
+            use_pairs = f[0] == 'p';
+            use128 = f[1] == '1';
+        }
+    }
 
     CUtensorMap ta, tw;
     uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M};
@@ -332,7 +439,9 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     if (st != FBB_OK) return st;
     uint64_t dims_w[2] = {(uint64_t)K, (uint64_t)N};
     int64_t str_w[2] = {1, ldw};
-    uint32_t box_w[2] = {BK, (uint32_t)(swiglu ? 128 : (use128 ? 128 : 256))};
+    // W box: the rows one CTA loads per k-block (a pair member loads half of the tile's rows; SwiGLU loads 128-row boxes)
+    const uint32_t w_rows = swiglu ? 128u : (use128 ? 128u : 256u);
+    uint32_t box_w[2] = {BK, use_pairs && !swiglu ? w_rows / 2 : w_rows};
     st = make_tmap_f16(&tw, W, 2, dims_w, str_w, box_w);
     if (st != FBB_OK) return st;
 
@@ -343,9 +452,14 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     st = make_tmap_f16(&tc, C, 2, dims_c, str_c, box_c, CU_TENSOR_MAP_SWIZZLE_64B);
     if (st != FBB_OK) return st;
 
-    if (swiglu) return launch_variant<256, true>(ta, tw, tc, g, stream);
-    if (use128) return launch_variant<128, false>(ta, tw, tc, g, stream);
-    return launch_variant<256, false>(ta, tw, tc, g, stream);
+    if (use_pairs) {
+        if (swiglu) return launch_variant<256, true, true>(ta, tw, tc, g, stream);
+        if (use128) return launch_variant<128, false, true>(ta, tw, tc, g, stream);
+        return launch_variant<256, false, true>(ta, tw, tc, g, stream);
+    }
+    if (swiglu) return launch_variant<256, true, false>(ta, tw, tc, g, stream);
+    if (use128) return launch_variant<128, false, false>(ta, tw, tc, g, stream);
+    return launch_variant<256, false, false>(ta, tw, tc, g, stream);
 }
 
 }  // namespace fbb

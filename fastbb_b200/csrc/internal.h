@@ -30,19 +30,36 @@ int num_sms();  // SM count of the current device
 // Launch with programmatic stream serialization (see grid_dependency_wait in common.cuh). FBB_NO_PDL=1 in the environment
 // turns the attribute off (plain stream order).
 bool pdl_enabled();
+// cluster_x > 1 launches thread-block clusters of that many CTAs along x (the grid must be a multiple of it).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+inline cudaError_t launch_pdl_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster_x,
+                                      Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    return launch_pdl_cluster(kern, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 
 int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
@@ -51,6 +68,9 @@ int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64
 int launch_linear(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
                   cudaStream_t stream);
+
+// How many CTA pairs (clusters of two) of the linear kernel with `bn`-column tiles fit on the current device at once.
+int linear_max_pairs(int bn);
 
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
                    const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, cudaStream_t stream);

@@ -69,6 +69,10 @@ const char* fbb_last_error(void);
  * wait (its output is then undefined), or a cudaError_t. Meant for tests and debugging, never for the hot path. */
 int fbb_device_status(unsigned int out[4]);
 
+/* Diagnostics: how many two-CTA clusters of the linear kernel (tile_columns = 128 or 256) the current device can hold at
+ * once; 0 means the kernel runs in its one-CTA form. No counterpart in the reference (its GEMMs are cuBLAS calls). */
+int fbb_linear_max_cta_pairs(int tile_columns);
+
 /* y[m, :] = LayerNorm(x[m, :]) * w + b, statistics in fp32, output fp16.
  * Replaces: the nn.LayerNorm calls of fastbb/vit.py:114,126,130,139,159,166,170 (norm1 / norm2) and :184,241 (vit.norm).
  * x: [M, C] of in_dtype with row stride ldx; y: [M, C] fp16 with row stride ldy; w, b: [C] of param_dtype or null.
