@@ -9,12 +9,16 @@
 //                   soon as the softmax group holds the previous S_t in registers; once the group has written P_t
 //                   (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the MN-major B operand,
 //                   8 x K16); O_t stays in tensor memory (fp32) over all key blocks
-//   warps 4..7/8..11 softmax group t: one thread per query row (tcgen05.ld 32x32b hands a thread its whole row, so the
-//                   row maximum and the row sum need no shuffles). The whole 128-key row of S is loaded at once, the
+//   warps 4..11/12..19 softmax group t, 16 query rows per warp: tcgen05.ld 16x256b hands thread i the key pairs
+//                   8k + 2(i%4), +1 of rows i/4 and i/4 + 8 (the m16n8 accumulator fragment), so a row's maximum and sum
+//                   take two shuffles among the four threads that share it, and P (fp16 pairs) goes back with the
+//                   matching 16x128b store. The 128-key block is loaded at once and S is released immediately; the
 //                   maximum is taken with 3-input max, p = 2^(s*scale*log2e - m) with packed f32x2 FMAs.
 //                   The running maximum m is only raised when a block exceeds it by more than 2^8 (then O_t and the
 //                   running sum are rescaled in place, a rare event after the first blocks); otherwise P is taken
 //                   relative to the older maximum, which keeps it <= 256 and exactly as accurate in fp16.
+//                   Four softmax warps share each SM sub-partition and cover one another's waits (measured against
+//                   one-thread-per-row groups of four warps: 740 -> 849 TFLOP/s at N = 16385).
 // With NQ = 2 the two groups alternate on the tensor core (S of one tile is computed while the other tile is in its
 // softmax). Variants (fastbb/attention.py:5-7) select the accumulate type of S: ff / fh -> fp32 S, hh -> fp16 S (an f16
 // tensor-memory accumulator, read back as half2 pairs); the softmax arithmetic is fp32 in both, as in the reference.
@@ -33,17 +37,17 @@ constexpr int kKVStages = 4;
 constexpr int kTileBytes = 128 * 64 * 2;  // one [128 x 64] fp16 tile
 constexpr float kLazyMax = 8.0f;          // raise the running maximum only beyond 2^8
 // Which of every 8 consecutive key pairs get their exponentials from the polynomial on the FMA pipes (bit i = pair i).
-// Measured on B200 (N = 16385, 16 heads): mask 0 -> 769, 0x88 -> 781, 0xAA -> 618 TFLOP/s: the extra FMA / ALU
+// Measured on B200 (N = 16385, 16 heads): mask 0 -> 849, 0x88 -> 841, 0xAA -> 700 TFLOP/s: the extra FMA / ALU
 // instructions cost what the transcendental unit saves, so the shipped default is 0 (the code path stays for tuning).
 #ifndef FBB_EMU_MASK
 #define FBB_EMU_MASK 0x00u
 #endif
 constexpr unsigned kEmuMask = FBB_EMU_MASK;  // e.g. 0x88: pairs 3 and 7 of 8 (25 %); 0: all on the transcendental unit
-// Register split of the 384-thread (NQ = 2) kernel. It is launched with 168 registers per thread (the most 12 warps can
+// Register split of the 640-thread (NQ = 2) kernel. It is launched with 96 registers per thread (the most 20 warps can
 // get); setmaxnreg.inc WAITS until the CTA's own pool has the registers, so the split must fit in that pool or the
-// kernel never starts its softmax: 128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168.
-constexpr int kRegsCtl = 72, kRegsSoftmax = 216;
-static_assert(128 * kRegsCtl + 256 * kRegsSoftmax <= 384 * 168, "setmaxnreg split exceeds the CTA's register pool");
+// kernel never starts its softmax: 128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96.
+constexpr int kRegsCtl = 40, kRegsSoftmax = 104;
+static_assert(128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96, "setmaxnreg split exceeds the CTA's register pool");
 
 // tensor-memory columns
 constexpr uint32_t kColS = 0;      // S_t at kColS + t*128 (128 columns each)
@@ -82,7 +86,7 @@ struct FlashArgs {
 };
 
 template <int NQ, bool S16>
-__global__ void __launch_bounds__(128 + 128 * NQ, 1)
+__global__ void __launch_bounds__(128 + 256 * NQ, 1)
 flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FlashArgs a) {
     using S = FlashSmem;
@@ -120,9 +124,9 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(s_full(t), 1);
-            mbar_init(p_ready(t), 4);
+            mbar_init(p_ready(t), 8);
             mbar_init(pv_done(t), 1);
-            mbar_init(s_free(t), 4);
+            mbar_init(s_free(t), 8);
         }
         *s_abort = 0;
         fence_barrier_init();
@@ -227,26 +231,33 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
     }
     } else {
-        // ------------------------------------------------------------------ softmax groups: one thread per query row
+        // ------------------------------------------------------------------ softmax groups
+        // Eight warps per tile, 16 query rows per warp (tensor-memory lanes 32*(u%4) + 16*(u/4) ..+15), read with the
+        // 16x256b shape: thread i holds, for rows i/4 and i/4 + 8, the key pairs 8k + 2*(i%4), +1 (k = 0..15) - the
+        // m16n8 accumulator fragment. Row maxima and sums are finished with two shuffles inside the four threads that
+        // share a row; P goes back with the 16x128b shape, whose layout is exactly those key pairs as fp16x2.
+        // Four softmax warps per SM sub-partition keep the transcendental unit busy across one another's waits.
         if constexpr (NQ == 2) setmaxnreg_inc<kRegsSoftmax>();
-        const int t = (warp - 4) >> 2;
-        const int quad = warp & 3;
-        const int row = q0 + t * FQ + quad * 32 + lane;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const int u = (warp - 4) & 7;
+        const int t = (warp - 4) >> 3;
+        const int lane_base = (u & 3) * 32 + (u >> 2) * 16;      // first tensor-memory lane (= row in the tile) of this warp
+        const int cq = lane & 3;
+        const int rowA = q0 + t * FQ + lane_base + (lane >> 2);  // this thread's rows: rowA and rowA + 8
+        const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16);
         const uint32_t tS = lane_addr + kColS + t * 128;
         const uint32_t tO = lane_addr + kColO + t * 64;
         const uint32_t tP = lane_addr + kColP + t * 64;
         const float sl = a.scale_log2;
-        float m_ref = -INFINITY, l_run = 0.f;
+        float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;  // running maximum and (this thread's share of the) sum
         bool ok = true;
-        // A warp whose 32 rows all lie beyond N (the padding of the last tile) only keeps the barriers moving: the
-        // rows of P, S and O it would touch feed nothing that is stored.
-        const bool warp_has_rows = q0 + t * FQ + quad * 32 < a.N;
+        // A warp whose 16 rows all lie beyond N (the padding of the last tile) only keeps the barriers moving.
+        const bool warp_has_rows = q0 + t * FQ + lane_base < a.N;
 
         for (int j = 0; j < nkb; ++j) {
-            if (quad == 0) FBB_TRACE(t, j, 0);
+            if (u == 0) FBB_TRACE(t, j, 0);
             if (!mbar_wait(s_full(t), j & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, t)) { ok = false; break; }
             tc_fence_after();
+            if (u == 0) FBB_TRACE(t, j, 1);
             if (!warp_has_rows) {
                 // S_t(j+1) can be ready long before the other warps have written P_t(j): this warp's arrival for block
                 // j must not land in the phase of block j-1, so it watches that phase complete first.
@@ -259,136 +270,118 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 continue;
             }
-            if (quad == 0) FBB_TRACE(t, j, 1);
-            const int key0 = j * FK;
-            const bool tail = key0 + FK > a.N;
-            // ---- load the whole row of S (fp32: 128 registers; fp16 accumulator: 64 registers of half2 pairs) and take
-            //      its maximum
-            constexpr int kRegs = S16 ? 64 : 128;
-            uint32_t r[kRegs];
-            float mx;
+            const int key0 = j * FK + 2 * cq;
+            const bool tail = j * FK + FK > a.N;
+            uint32_t r[64];
+            tmem_ld_16x256b_x16(tS, r);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
+            float va[64];
             if constexpr (!S16) {
-                tmem_ld32(tS, r);
-                tmem_ld32(tS + 32, r + 32);
-                tmem_ld32(tS + 64, r + 64);
-                tmem_ld32(tS + 96, r + 96);
-                tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
-                if (tail) {
 #pragma unroll
-                    for (int i = 0; i < 128; ++i)
-                        if (key0 + i >= a.N) r[i] = 0xFF800000u;  // -inf
-                }
-                float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]), mx2 = __uint_as_float(r[2]), mx3 = __uint_as_float(r[3]);
-#pragma unroll
-                for (int i = 4; i < 128; i += 8) {
-                    mx0 = fmax3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                    mx1 = fmax3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-                    if (i + 4 < 128) {
-                        mx2 = fmax3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-                        mx3 = fmax3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
-                    }
-                }
-                mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl;
+                for (int i = 0; i < 64; ++i) va[i] = __uint_as_float(r[i]);
             } else {
-                tmem_ld32_pack16(tS, r);
-                tmem_ld32_pack16(tS + 64, r + 32);
-                tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
-                if (tail) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        if (key0 + 2 * i >= a.N) r[i] = (r[i] & 0xFFFF0000u) | 0xFC00u;          // low half -> -inf
-                        if (key0 + 2 * i + 1 >= a.N) r[i] = (r[i] & 0x0000FFFFu) | 0xFC000000u;  // high half -> -inf
-                    }
-                }
-                __half2 mxa = *reinterpret_cast<const __half2*>(&r[0]), mxb = *reinterpret_cast<const __half2*>(&r[1]);
-#pragma unroll
-                for (int i = 2; i < 64; i += 2) {
-                    mxa = __hmax2(mxa, *reinterpret_cast<const __half2*>(&r[i]));
-                    mxb = __hmax2(mxb, *reinterpret_cast<const __half2*>(&r[i + 1]));
-                }
-                mxa = __hmax2(mxa, mxb);
-                mx = fmaxf(__low2float(mxa), __high2float(mxa)) * sl;
+                for (int i = 0; i < 64; ++i) va[i] = __half2float(__ushort_as_half((unsigned short)(r[i] & 0xFFFFu)));
             }
-            if (quad == 0) FBB_TRACE(t, j, 2);
+            if (tail) {
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    if (key0 + 8 * k >= a.N) va[4 * k] = va[4 * k + 2] = -INFINITY;
+                    if (key0 + 8 * k + 1 >= a.N) va[4 * k + 1] = va[4 * k + 3] = -INFINITY;
+                }
+            }
+            float mxA = fmaxf(va[0], va[1]), mxB = fmaxf(va[2], va[3]);
+#pragma unroll
+            for (int k = 1; k < 16; ++k) {
+                mxA = fmax3(mxA, va[4 * k], va[4 * k + 1]);
+                mxB = fmax3(mxB, va[4 * k + 2], va[4 * k + 3]);
+            }
+            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2)) * sl;
+            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2)) * sl;
+            if (u == 0) FBB_TRACE(t, j, 2);
             // O_t and P_t are still being read by P_t(j-1) . V until that product has completed (normally long ago)
             if (j > 0) {
                 if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
                 tc_fence_after();
             }
-            // ---- running maximum: raised only when this block exceeds it by more than 2^kLazyMax
+            // ---- running maxima: raised only when this block exceeds them by more than 2^kLazyMax
             if (j == 0) {
-                m_ref = mx;
-            } else if (__any_sync(0xffffffffu, mx > m_ref + kLazyMax)) {
-                const float m_new = fmaxf(m_ref, mx);
-                const float c = ex2_approx(m_ref - m_new);
+                mA = mxA;
+                mB = mxB;
+            } else if (__any_sync(0xffffffffu, mxA > mA + kLazyMax || mxB > mB + kLazyMax)) {
+                const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+                const float cA = ex2_approx(mA - nA), cB = ex2_approx(mB - nB);
+                uint32_t o[32];
+                tmem_ld_16x256b_x8(tO, o);
+                tmem_wait_ld();
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t o[32];
-                    tmem_ld32(tO + 32u * half, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * c);
-                    tmem_st32(tO + 32u * half, o);
+                for (int k = 0; k < 8; ++k) {
+                    o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA);
+                    o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA);
+                    o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB);
+                    o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB);
                 }
-                l_run *= c;
-                m_ref = m_new;
+                tmem_st_16x256b_x8(tO, o);
+                lA *= cA;
+                lB *= cB;
+                mA = nA;
+                mB = nB;
             }
-            // ---- p = 2^(s*sl - m) in fp32 for both accumulate types; kEmuEvery-th pair on the FMA pipes, the others on
-            //      the transcendental unit; row sum in fp32; P as fp16 pairs back to tensor memory
-            const float2 sl2 = make_float2(sl, sl), nm2 = make_float2(-m_ref, -m_ref);
-            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+            // ---- p = 2^(s*sl - m) in fp32; row sums in fp32; P as fp16 pairs back to tensor memory
+            const float2 sl2 = make_float2(sl, sl), nmA = make_float2(-mA, -mA), nmB = make_float2(-mB, -mB);
+            float2 accA = make_float2(0.f, 0.f), accB = make_float2(0.f, 0.f);
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float2 sv;
-                    if constexpr (!S16) sv = make_float2(__uint_as_float(r[32 * c + 2 * i]), __uint_as_float(r[32 * c + 2 * i + 1]));
-                    else sv = __half22float2(*reinterpret_cast<const __half2*>(&r[16 * c + i]));
-                    const float2 x = ffma2(sv, sl2, nm2);
-                    float2 p;
-                    if ((kEmuMask >> (i & 7)) & 1) p = exp2_emulated(x);
-                    else p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-                    if (i & 1) acc1 = fadd2(acc1, p); else acc0 = fadd2(acc0, p);
-                    pk[i] = pack_h2(p.x, p.y);
+            for (int k = 0; k < 16; ++k) {
+                const float2 xA = ffma2(make_float2(va[4 * k], va[4 * k + 1]), sl2, nmA);
+                const float2 xB = ffma2(make_float2(va[4 * k + 2], va[4 * k + 3]), sl2, nmB);
+                float2 pA, pB;
+                if ((kEmuMask >> (k & 7)) & 1) {  // this key pair on the FMA pipes instead of the transcendental unit
+                    pA = exp2_emulated(xA);
+                    pB = exp2_emulated(xB);
+                } else {
+                    pA = make_float2(ex2_approx(xA.x), ex2_approx(xA.y));
+                    pB = make_float2(ex2_approx(xB.x), ex2_approx(xB.y));
                 }
-                tmem_st16(tP + 16u * c, pk);
+                accA = fadd2(accA, pA);
+                accB = fadd2(accB, pB);
+                pk[2 * k] = pack_h2(pA.x, pA.y);
+                pk[2 * k + 1] = pack_h2(pB.x, pB.y);
             }
-            const float sum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
-            if (quad == 0) FBB_TRACE(t, j, 3);
+            tmem_st_16x128b_x16(tP, pk);
+            if (u == 0) FBB_TRACE(t, j, 3);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready(t));
-            if (quad == 0) FBB_TRACE(t, j, 4);
-            l_run += sum;
+            if (u == 0) FBB_TRACE(t, j, 4);
+            lA += accA.x + accA.y;
+            lB += accB.x + accB.y;
         }
         if (ok && warp_has_rows && mbar_wait(pv_done(t), (uint32_t)(nkb - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
             tc_fence_after();
-            const float inv = 1.f / l_run;
-            __half* dst = a.o + (int64_t)b * a.o_sb + (int64_t)row * a.o_sn + (int64_t)h * a.o_sh;
+            // a row's sum is spread over the four threads that share it
+            lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+            lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+            lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+            lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+            const float invA = 1.f / lA, invB = 1.f / lB;
+            uint32_t o[32];
+            tmem_ld_16x256b_x8(tO, o);
+            tmem_wait_ld();
+            __half* dstA = a.o + (int64_t)b * a.o_sb + (int64_t)rowA * a.o_sn + (int64_t)h * a.o_sh + 2 * cq;
+            __half* dstB = dstA + 8 * a.o_sn;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t o[32];
-                tmem_ld32(tO + 32u * half, o);
-                tmem_wait_ld();
-                if (row < a.N) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 u;
-                        u.x = pack_h2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        u.y = pack_h2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        u.z = pack_h2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        u.w = pack_h2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + 32 * half + 8 * v) = u;
-                    }
-                }
+            for (int k = 0; k < 8; ++k) {
+                if (rowA < a.N)
+                    *reinterpret_cast<uint32_t*>(dstA + 8 * k) = pack_h2(__uint_as_float(o[4 * k]) * invA, __uint_as_float(o[4 * k + 1]) * invA);
+                if (rowA + 8 < a.N)
+                    *reinterpret_cast<uint32_t*>(dstB + 8 * k) = pack_h2(__uint_as_float(o[4 * k + 2]) * invB, __uint_as_float(o[4 * k + 3]) * invB);
             }
         }
     }
@@ -415,7 +408,7 @@ static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, co
         configured[dev] = true;
     }
     dim3 grid((unsigned)((a.N + FQ * NQ - 1) / (FQ * NQ)), (unsigned)(B * a.H), 1);
-    cudaError_t e = launch_pdl(kern, grid, dim3(128 + 128 * NQ), FlashSmem::kDynamic, stream, tq, tk, tv, a);
+    cudaError_t e = launch_pdl(kern, grid, dim3(128 + 256 * NQ), FlashSmem::kDynamic, stream, tq, tk, tv, a);
     if (e != cudaSuccess) return fail((int)e, "flash64_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }
