@@ -102,6 +102,94 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const void* __restr
     }
 }
 
+
+// Fast path for fp16 input and fp16 affine parameters: one warp normalises TWO rows at a time, and every global load of
+// the iteration (both rows and the parameter vectors) is issued before the first reduction, so a warp has 3*NV 16-byte
+// loads in flight instead of NV and the parameter fetch no longer waits behind the statistics. Rows are kept as raw
+// fp16 vectors (16 registers for C = 1024) and converted in each of the three register passes.
+template <int NV>
+__global__ void __launch_bounds__(128) layernorm_rows2_f16_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                                 const __half* __restrict__ w, const __half* __restrict__ b,
+                                                                 int64_t M, int C, int64_t ldx, int64_t ldy, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row0 = 2 * ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+    grid_dependency_wait();
+    if (row0 >= M) return;
+    const bool two = row0 + 1 < M;
+    const int nvec = C >> 3;
+    uint4 xa[NV], xb[NV], gw[NV], gb[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        const bool in = vi < nvec;
+        xa[i] = in ? __ldg(reinterpret_cast<const uint4*>(x + row0 * ldx) + vi) : make_uint4(0, 0, 0, 0);
+        xb[i] = (in && two) ? __ldg(reinterpret_cast<const uint4*>(x + (row0 + 1) * ldx) + vi) : make_uint4(0, 0, 0, 0);
+        gw[i] = (in && w != nullptr) ? __ldg(reinterpret_cast<const uint4*>(w) + vi) : make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
+        gb[i] = (in && b != nullptr) ? __ldg(reinterpret_cast<const uint4*>(b) + vi) : make_uint4(0, 0, 0, 0);
+    }
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const __half2* ha = reinterpret_cast<const __half2*>(&xa[i]);
+        const __half2* hb = reinterpret_cast<const __half2*>(&xb[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 fa = __half22float2(ha[j]), fb = __half22float2(hb[j]);
+            sa += fa.x + fa.y;
+            sb += fb.x + fb.y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, o);
+        sb += __shfl_xor_sync(0xffffffffu, sb, o);
+    }
+    const float inv_c = 1.f / (float)C;
+    const float ma = sa * inv_c, mb = sb * inv_c;
+    float qa = 0.f, qb = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < nvec) {
+            const __half2* ha = reinterpret_cast<const __half2*>(&xa[i]);
+            const __half2* hb = reinterpret_cast<const __half2*>(&xb[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __half22float2(ha[j]), fb = __half22float2(hb[j]);
+                qa += (fa.x - ma) * (fa.x - ma) + (fa.y - ma) * (fa.y - ma);
+                qb += (fb.x - mb) * (fb.x - mb) + (fb.y - mb) * (fb.y - mb);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        qa += __shfl_xor_sync(0xffffffffu, qa, o);
+        qb += __shfl_xor_sync(0xffffffffu, qb, o);
+    }
+    const float ra = rsqrtf(qa * inv_c + eps), rb = rsqrtf(qb * inv_c + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nvec) {
+            const __half2* ha = reinterpret_cast<const __half2*>(&xa[i]);
+            const __half2* hb = reinterpret_cast<const __half2*>(&xb[i]);
+            const __half2* hw = reinterpret_cast<const __half2*>(&gw[i]);
+            const __half2* hbias = reinterpret_cast<const __half2*>(&gb[i]);
+            uint4 oa, ob;
+            uint32_t* pa = reinterpret_cast<uint32_t*>(&oa);
+            uint32_t* pb = reinterpret_cast<uint32_t*>(&ob);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __half22float2(ha[j]), fb = __half22float2(hb[j]);
+                const float2 g = __half22float2(hw[j]), be = __half22float2(hbias[j]);
+                pa[j] = pack_h2(fmaf((fa.x - ma) * ra, g.x, be.x), fmaf((fa.y - ma) * ra, g.y, be.y));
+                pb[j] = pack_h2(fmaf((fb.x - mb) * rb, g.x, be.x), fmaf((fb.y - mb) * rb, g.y, be.y));
+            }
+            *(reinterpret_cast<uint4*>(y + row0 * ldy) + vi) = oa;
+            if (two) *(reinterpret_cast<uint4*>(y + (row0 + 1) * ldy) + vi) = ob;
+        }
+    }
+}
+
 // Any C % 8 == 0 (rows longer than 2048): three passes over the row, the second and third served by L1/L2.
 __global__ void __launch_bounds__(256) layernorm_long_rows_kernel(const void* __restrict__ x, __half* __restrict__ y,
                                                                  const void* __restrict__ w, const void* __restrict__ b,
@@ -153,6 +241,26 @@ int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64
     const int nv = (C / 8 + 31) / 32;
     __half* yh = reinterpret_cast<__half*>(y);
     cudaError_t err = cudaSuccess;
+    if (in_dtype == FBB_DTYPE_F16 && param_dtype == FBB_DTYPE_F16 && nv >= 1 && nv <= 6) {
+        const __half* xh = reinterpret_cast<const __half*>(x);
+        const __half* wh = reinterpret_cast<const __half*>(w);
+        const __half* bh = reinterpret_cast<const __half*>(b);
+        const unsigned grid2 = (unsigned)((M + 7) / 8);  // 4 warps x 2 rows per block
+#define FBB_LN2_CASE(N)                                                                                              \
+    case N:                                                                                                          \
+        err = launch_pdl(layernorm_rows2_f16_kernel<N>, dim3(grid2), dim3(128), 0, stream, xh, yh, wh, bh, M, C, ldx, ldy, eps); \
+        break;
+        switch (nv) {
+            FBB_LN2_CASE(1)
+            FBB_LN2_CASE(2)
+            FBB_LN2_CASE(3)
+            FBB_LN2_CASE(4)
+            FBB_LN2_CASE(5)
+            FBB_LN2_CASE(6)
+        }
+#undef FBB_LN2_CASE
+        return cuda_status(err);
+    }
 #define FBB_LN_CASE(N)                                                                                              \
     case N:                                                                                                         \
         err = launch_pdl(layernorm_rows_kernel<N>, dim3(grid), dim3(warps * 32), 0, stream, x, yh, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype); \
