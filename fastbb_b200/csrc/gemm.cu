@@ -425,9 +425,10 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
         if (c < best) { best = c; use_pairs = true; use128 = false; }
     }
     if (const char* f = getenv("FBB_GEMM_FORCE")) {
-        if (!swiglu && (f[0] == 's' || (f[0] == 'p' && pairs256 > 0 && max_pairs<128, false>() > 0))) {
+        const bool want128 = f[0] != '\0' && f[1] == '1' && !swiglu;  // SwiGLU always uses 256-column tiles (x1 | x2 halves)
+        if (f[0] == 's' || (f[0] == 'p' && pairs256 > 0 && (!want128 || max_pairs<128, false>() > 0))) {
             use_pairs = f[0] == 'p';
-            use128 = f[1] == '1';
+            use128 = want128;
         }
     }
 

@@ -117,6 +117,33 @@ def test_linear_matches_oracle(oracle, M, N, K, act, has_bias, has_res, variant)
     status_ok()
 
 
+@pytest.mark.parametrize("form", ["s256", "s128", "p256", "p128"])
+def test_linear_every_tile_form_matches_oracle(oracle, form, monkeypatch):
+    """The kernel has four forms (one CTA or a CTA pair per tile, 256- or 128-column tiles) and picks one by a cost
+    model; this forces each of them on tail-heavy shapes, including the SwiGLU and fp16-accumulate epilogues."""
+    from fastbb_b200 import _lib
+    from fastbb_b200.gemm import linear
+    monkeypatch.setenv("FBB_GEMM_FORCE", form)
+    if form[0] == "p" and _lib.load().fbb_linear_max_cta_pairs(256) == 0:
+        pytest.skip("this device cannot co-schedule CTA pairs")
+    g = torch.Generator().manual_seed(99)
+    for M, N, K, act, variant in [(513, 1160, 200, "gelu", "f32"), (257, 384, 1536, None, "f32"), (1370, 1024, 264, "swiglu", "f32"),
+                                  (300, 520, 72, None, "h"), (1, 256, 64, None, "f32")]:
+        x = torch.randn(M, K, generator=g).half()
+        w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+        b = (0.1 * torch.randn(N, generator=g)).half()
+        n_out = N // 2 if act == "swiglu" else N
+        res = torch.randn(M, n_out, generator=g).half() if act is None else None
+        gam = (0.05 + 0.15 * torch.rand(n_out, generator=g)).half() if act is None else None
+        out, check = padded((M, n_out))
+        d = lambda t: None if t is None else t.to(dev())  # noqa: E731
+        y = linear(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant=variant, out=out)
+        want = oracle.linear(x, w, b, act=act, res=res, gamma=gam)
+        assert oracle.rel_l2(y.cpu().float(), want) < (TOL_F16 if variant == "h" else TOL_F32), (form, M, N, K, act)
+        check()
+    status_ok()
+
+
 def test_linear_against_reference_outputs(oracle):
     """Same seeded inputs as tests/golden/make_golden.py; the stored outputs come from the reference's gemm.linear."""
     from fastbb_b200.gemm import linear
