@@ -32,6 +32,8 @@ PROTOTYPES = {
     "fbb_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _f32, _i32, _i32, _vp]),
     "fbb_linear_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
+    "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "fbb_flash64_f16_ws": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp, _i64, _vp]),
 }
 
 

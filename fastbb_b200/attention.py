@@ -9,6 +9,11 @@ variant: "hh" fp16-accumulate QK^T and PV (fastest), "fh" fp32 QK^T + fp16 PV, "
 Small inputs run the same kernel with one 128-query tile per CTA instead of the reference's SDPA fallback
 (fastbb/vit.py:146-150); anything the kernel does not cover (other head dims, dtypes, strides, CPU tensors,
 scale <= 0) raises instead of falling back to torch (fastbb/attention.py:38-48).
+
+When the query tiles do not fill the SMs evenly (ViT-L/14 at 896x1344: 400 CTAs of work on 148 SMs) the kernel runs in
+its split form, which needs ~11 MB of scratch memory: `attention` keeps one zero-initialised workspace per (device,
+stream) for that and hands it to fbb_flash64_f16_ws; `workspace=False` selects the plain one-CTA-per-tile form,
+`workspace=<uint8 CUDA tensor>` lends a caller-owned (zeroed) one.
 """
 import torch
 
@@ -21,7 +26,18 @@ def _ok(t):
             and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0)
 
 
-def attention(q, k, v, scale=None, out=None, variant="hh", rows=None):
+_WORKSPACES = {}  # (device index, stream handle) -> zeroed uint8 tensor; the kernel leaves it zeroed after every launch
+
+
+def _workspace(device, need):
+    key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _WORKSPACES[key] = torch.zeros(need, device=device, dtype=torch.uint8)
+    return ws
+
+
+def attention(q, k, v, scale=None, out=None, variant="hh", rows=None, workspace=None):
     """q, k, v [B, N, H, 64] -> [B, N, H, 64]. `rows` (the reference's CTA-height override) is accepted and ignored."""
     B, N, H, D = q.shape
     if out is not None and (out.shape != (*q.shape[:-1], v.shape[-1]) or out.device != q.device or out.dtype != q.dtype):
@@ -41,15 +57,25 @@ def attention(q, k, v, scale=None, out=None, variant="hh", rows=None):
     if B == 0 or N == 0 or H == 0:
         return out
     with _on(q.device):
-        _lib.check(_lib.load().fbb_flash64_f16(
+        lib = _lib.load()
+        ws_ptr, ws_bytes = None, 0
+        if workspace is not False:
+            need = lib.fbb_flash64_workspace_bytes(B, N, H)
+            if need > 0:
+                ws = _workspace(q.device, need) if workspace is None else workspace
+                if not (ws.is_cuda and ws.device == q.device and ws.dtype == torch.uint8 and ws.is_contiguous() and ws.numel() >= need):
+                    raise ValueError(f"workspace must be a contiguous uint8 tensor of >= {need} bytes on {q.device}")
+                ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(lib.fbb_flash64_f16_ws(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, N, H,
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
-            float(scale), _lib.FLASH_VARIANT[variant], _lib.stream_ptr(q.device)))
+            float(scale), _lib.FLASH_VARIANT[variant], ws_ptr, ws_bytes, _lib.stream_ptr(q.device)))
     _lib.launched()
     return out
 
 
-def attention_bhnd(q, k, v, scale=None, variant="hh"):
+def attention_bhnd(q, k, v, scale=None, variant="hh", workspace=None):
     """SDPA-layout drop-in: q, k, v [B, H, N, 64] -> [B, H, N, 64] (strided views, no copies)."""
-    return attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale, variant=variant).transpose(1, 2)
+    return attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale, variant=variant,
+                     workspace=workspace).transpose(1, 2)

@@ -151,9 +151,12 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
     return launch_linear(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, (cudaStream_t)stream);
 }
 
-int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
-                    int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
-                    int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream) {
+int64_t fbb_flash64_workspace_bytes(int B, int N, int H) { return flash64_workspace_bytes_for(B, N, H); }
+
+int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                       int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                       int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace, int64_t workspace_bytes,
+                       void* stream) {
     if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(FBB_ERR_NULL, "flash64: q, k, v or o is null");
     if (variant < FBB_FLASH_FF || variant > FBB_FLASH_HH) return fail(FBB_ERR_ENUM, "flash64: unknown variant %d", variant);
     if (B < 0 || N < 0 || H <= 0 || (int64_t)B * H > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: bad B/N/H (%d, %d, %d)", B, N, H);
@@ -164,8 +167,16 @@ int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B,
             return fail(FBB_ERR_ALIGN, "flash64: strides must be non-negative multiples of 8 elements");
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(FBB_ERR_ALIGN, "flash64: pointers must be 16-byte aligned");
     if (q_sn < 64 || k_sn < 64 || v_sn < 64 || o_sn < 64) return fail(FBB_ERR_SHAPE, "flash64: token stride smaller than the head dimension");
+    if (workspace != nullptr && (!aligned16(workspace) || workspace_bytes < 0)) return fail(FBB_ERR_ALIGN, "flash64: workspace must be 16-byte aligned");
     if (B == 0 || N == 0) return FBB_OK;
-    return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, (cudaStream_t)stream);
+    return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                    int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                    int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream) {
+    return fbb_flash64_f16_ws(q, k, v, o, B, N, H, q_sb, q_sn, q_sh, k_sb, k_sn, k_sh, v_sb, v_sn, v_sh, o_sb, o_sn, o_sh, scale, variant,
+                              nullptr, 0, stream);
 }
 
 }  // extern "C"

@@ -3,12 +3,25 @@
 // SDPA fallback for small inputs (fastbb/vit.py:146-150). Q, K, V are read in place from the strided [b, n, h, 64]
 // views of the packed qkv GEMM output; O is written as [b, n, h*64].
 //
-// One CTA owns NQ (1 or 2) tiles of 128 queries of one (batch, head) and walks the keys in blocks of 128:
-//   warp 0          TMA producer: Q tiles once, then K_j and V_j into a ring of stages (128-byte swizzle, zero fill)
+// Work: a "tile group" is NQ (1 or 2) tiles of 128 queries of one (batch, head); it walks the keys in blocks of 128, so
+// the whole problem is groups x key blocks "units". Without a workspace every CTA takes exactly one group. With a
+// workspace, and when the groups do not fill the SMs evenly, the grid is persistent (one CTA per SM): every CTA first
+// takes whole groups round-robin (group = round * G + cta, so CTAs running together share heads, i.e. K/V tiles in L2)
+// for all but the last full wave, then an equal share of the units of what is left (between one and two waves' worth,
+// so a share is at least one group long and a group is split over at most two CTAs):
+//   - the CTA whose share starts in the middle of a group (always the first item of its share) leaves the unnormalised
+//     O (fp32), the running maxima and sums in its workspace slot and raises the slot's per-warp flags;
+//   - the CTA that began that group (always the last item of its share, so it needs the slot late) merges the slot into
+//     its own accumulators, clears the flags and writes the rows.
+// With 400 groups on 148 SMs (ViT-L/14 at 896x1344) this replaces 3 waves by 2.7: fp16-S variant 243 -> 215 us per
+// launch; the fp32-S variant stays at ~201 us because the two tiles of a long-lived CTA drift into step (see below).
+//
+//   warp 0          TMA producer: the Q tiles of each item, then K_j and V_j into a ring of stages (128-byte swizzle, zero fill)
 //   warps 1, 2      UMMA issuers, one per tile: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory, issued as
-//                   soon as the softmax group holds the previous S_t in registers; once the group has written P_t
-//                   (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the MN-major B operand,
-//                   8 x K16); O_t stays in tensor memory (fp32) over all key blocks
+//                   soon as the softmax group holds the previous S_t in registers - also across items, so the first
+//                   product of the next group overlaps the last softmax and the write-out of this one; once the group
+//                   has written P_t (fp16) back into tensor memory, O_t += P_t V_j (A from tensor memory, V as the
+//                   MN-major B operand, 8 x K16); O_t stays in tensor memory (fp32) over the key blocks of an item
 //   warps 4..11/12..19 softmax group t, 16 query rows per warp: tcgen05.ld 16x256b hands thread i the key pairs
 //                   8k + 2(i%4), +1 of rows i/4 and i/4 + 8 (the m16n8 accumulator fragment), so a row's maximum and sum
 //                   take two shuffles among the four threads that share it, and P (fp16 pairs) goes back with the
@@ -26,6 +39,11 @@
 // there would add N terms in fp16, where the reference's fh / hh only ever add 64 (one key block) before going to fp32.
 // The kernel is bound by the exponentials, not the tensor core: 128 x 128 of them per S tile against 16 results per
 // clock per SM from the transcendental unit is twice the time of the tile's two matrix products (1024 vs 2 x 256 clocks).
+// Measured dynamics worth knowing before changing the pipeline: a softmax warp alone cannot saturate the transcendental
+// unit, so the two tiles run fastest half a period apart (2800 clocks per unit); in step, every phase collides with its
+// twin (3800 clocks). The half-period offset set at start-up is not stable: over some tens of units the later tile
+// catches up. CTAs that live for one group (<= ~130 units) mostly keep it; the persistent form loses part of what it
+// gains from the removed wave this way. Forcing strict turns with an extra barrier pair costs more than it saves (3100).
 #include "common.cuh"
 #include "internal.h"
 
@@ -50,20 +68,34 @@ constexpr int kRegsCtl = 40, kRegsSoftmax = 104;
 static_assert(128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96, "setmaxnreg split exceeds the CTA's register pool");
 
 // tensor-memory columns
-constexpr uint32_t kColS = 0;      // S_t at kColS + t*128 (128 columns each)
-constexpr uint32_t kColO = 256;    // O_t at kColO + t*64 (fp32, 64 columns each)
-constexpr uint32_t kColP = 384;    // P_t at kColP + t*64 (fp16 pairs: 64 columns each)
+// tensor-memory columns of tile t: S_t (128 columns) at t * kColTileS, O_t (fp32, 64 columns) at kColO + t * kColTileOP,
+// P_t (fp16 pairs, 64 columns) kColP after O_t
+constexpr uint32_t kColTileS = 128, kColO = 256, kColTileOP = 64, kColP = 128;
 
 struct FlashSmem {
-    static constexpr int kQOff = 0;                                  // NQ x 16 KB
+    static constexpr int kQOff = 0;                                  // NQ (<= 2) tiles x 16 KB
     static constexpr int kKOff = 2 * kTileBytes;                     // stages x 16 KB
     static constexpr int kVOff = kKOff + kKVStages * kTileBytes;     // stages x 16 KB
     static constexpr int kBarOff = kVOff + kKVStages * kTileBytes;
-    // barriers: q_full, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_done[2], s_free[2]
-    static constexpr int kNumBars = 1 + 4 * kKVStages + 8;
-    static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
-    static constexpr int kDynamic = kBytes + 1024;
+    // barriers: q_full, q_empty, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_done[2], s_free[2]
+    static constexpr int kNumBars = 2 + 4 * kKVStages + 8;
+    static constexpr int kTailOff = kBarOff + kNumBars * 8 + 16;    // TailItems (40 bytes)
+    static constexpr int kBytes = kTailOff + 48;
+    // No slack for aligning by hand (the array is declared 1024-byte aligned): 160.4 KB keeps the CTA inside the 164 KB
+    // shared-memory configuration, which leaves 92 KB of L1 for the softmax warps' register spills. With 32 KB more
+    // (a second Q buffer was tried) the SM falls to 28 KB of L1 and the whole kernel runs 13 % slower.
+    static constexpr int kDynamic = kBytes;
 };
+
+// Workspace of the split form: per CTA one slot for the group it starts in the middle. A slot holds, for each of the 16
+// softmax warps, 36 values per lane stored [value][lane] (32 accumulator registers of the 16x256b fragment, then the two
+// running maxima and the lane's shares of the two running sums), preceded by one flag word per warp.
+constexpr int kSlotWarps = 16;
+constexpr int kSlotValues = 36;
+constexpr size_t kSlotFloats = (size_t)kSlotWarps * kSlotValues * 32;
+constexpr size_t kFlagBytesPerCta = kSlotWarps * sizeof(unsigned);
+static size_t flag_region_bytes(int ctas) { return ((size_t)ctas * kFlagBytesPerCta + 255) & ~(size_t)255; }
+int64_t flash64_workspace_bytes();
 
 #ifdef FBB_FLASH_TRACE
 // Development aid: per-iteration clock stamps of one softmax warp (CTA 0, lane 0 of warps 4 and 8) and of the UMMA
@@ -71,7 +103,7 @@ struct FlashSmem {
 __device__ long long* g_flash_trace = nullptr;
 #define FBB_TRACE(slot, j, k)                                                                                         \
     do {                                                                                                              \
-        if (g_flash_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (j) < 64)                   \
+        if (g_flash_trace != nullptr && blockIdx.x == 0 && lane == 0 && (j) < 64)                                      \
             g_flash_trace[((slot) * 64 + (j)) * 8 + (k)] = clock64();                                                   \
     } while (0)
 #else
@@ -83,43 +115,90 @@ struct FlashArgs {
     int N, H;
     int64_t o_sb, o_sn, o_sh;
     float scale_log2;
+    int groups_per_head;     // ceil(N / (128 * NQ))
+    int nkb;                 // key blocks per group
+    int rounds;              // whole groups every CTA takes round-robin before the tail region
+    long long tail_units;    // (groups - rounds * gridDim.x) * nkb, dealt out in equal contiguous shares
+    unsigned* ws_flags;      // [gridDim.x][16], all zero between launches; null when no group is ever split
+    float* ws_data;          // [gridDim.x][kSlotFloats]
 };
+
+// A CTA's work is a list of items (group w, key blocks [kb0, kb1)): first `rounds` whole groups taken round-robin
+// (group = round * G + cta, so that the CTAs running at the same time share heads, i.e. K/V tiles in L2), then its share
+// of the tail region, whose (group, key block) units are dealt out in contiguous runs of at least one group's length:
+// at most three items (the end of a group another CTA began, a whole group, the beginning of one the next CTA ends).
+// Thread 0 writes the tail items to shared memory once; every role walks the list by item index.
+struct TailItems {
+    int n;
+    int w[3], kb0[3], kb1[3];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Lane 0 polls a workspace flag until it is raised (bounded like every other wait); the result is warp-uniform.
+__device__ __forceinline__ bool wait_slot_flag(const unsigned* flag, int lane, volatile int* abort_flag, unsigned detail) {
+    bool ok = true;
+    if (lane == 0 && ld_acquire_gpu(flag) == 0u) {
+        const uint64_t t0 = globaltimer_ns();
+        for (;;) {
+            __nanosleep(200);
+            if (ld_acquire_gpu(flag) != 0u) break;
+            if (*abort_flag) { ok = false; break; }
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                report_error(DEV_TIMEOUT_OTHER, detail);
+                *abort_flag = 1;
+                __threadfence_block();
+                ok = false;
+                break;
+            }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok) != 0;
+    __syncwarp();
+    if (ok) (void)ld_acquire_gpu(flag);  // every lane orders its own reads of the slot after the flag
+    return ok;
+}
 
 template <int NQ, bool S16>
 __global__ void __launch_bounds__(128 + 256 * NQ, 1)
 flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FlashArgs a) {
     using S = FlashSmem;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    uint8_t* gen = smem_raw + (base - raw);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    uint8_t* gen = smem_raw;
     const uint32_t bar0 = base + S::kBarOff;
-    const uint32_t q_full = bar0;
-    auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
-    auto v_full = [&](int s) { return bar0 + 8u * (1 + kKVStages + s); };
-    auto k_empty = [&](int s) { return bar0 + 8u * (1 + 2 * kKVStages + s); };
-    auto v_empty = [&](int s) { return bar0 + 8u * (1 + 3 * kKVStages + s); };
-    auto s_full = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + t); };
-    auto p_ready = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 2 + t); };
-    auto pv_done = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 4 + t); };
-    auto s_free = [&](int t) { return bar0 + 8u * (1 + 4 * kKVStages + 6 + t); };
+    const uint32_t q_full = bar0, q_empty = bar0 + 8u;
+    auto k_full = [&](int s) { return bar0 + 8u * (2 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (2 + kKVStages + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (2 + 2 * kKVStages + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (2 + 3 * kKVStages + s); };
+    auto s_full = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + t); };
+    auto p_ready = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 2 + t); };
+    auto pv_done = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 4 + t); };
+    auto s_free = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 6 + t); };
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + S::kBarOff + S::kNumBars * 8);
     volatile int* s_abort = reinterpret_cast<volatile int*>(gen + S::kBarOff + S::kNumBars * 8 + 4);
+    TailItems* s_tail = reinterpret_cast<TailItems*>(gen + S::kTailOff);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int bh = blockIdx.y;
-    const int b = bh / a.H, h = bh % a.H;
-    const int q0 = blockIdx.x * (FQ * NQ);
-    const int nkb = (a.N + FK - 1) / FK;
+    const int nkb = a.nkb;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, NQ);  // one commit per tile issuer, after the item's last Q K^T
         for (int s = 0; s < kKVStages; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(v_full(s), 1);
-            mbar_init(k_empty(s), NQ);  // one commit per tile issuer
+            mbar_init(k_empty(s), NQ);
             mbar_init(v_empty(s), NQ);
         }
         for (int t = 0; t < 2; ++t) {
@@ -129,6 +208,23 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(s_free(t), 8);
         }
         *s_abort = 0;
+        // this CTA's share [tb, te) of the tail region's units, cut into items at group boundaries
+        long long tb = 0, te = 0;
+        if (a.tail_units > 0) {
+            tb = (long long)(((unsigned long long)a.tail_units * blockIdx.x) / gridDim.x);
+            te = (long long)(((unsigned long long)a.tail_units * (blockIdx.x + 1u)) / gridDim.x);
+        }
+        int n = 0;
+        for (long long uu = tb; uu < te && n < 3; ++n) {  // (no iterations without a tail region)
+            const int wt = (int)(uu / nkb);
+            const int kb0 = (int)(uu - (long long)wt * nkb);
+            const int kb1 = (int)((te - uu < (long long)(nkb - kb0)) ? kb0 + (te - uu) : nkb);
+            s_tail->w[n] = a.rounds * (int)gridDim.x + wt;
+            s_tail->kb0[n] = kb0;
+            s_tail->kb1[n] = kb1;
+            uu += kb1 - kb0;
+        }
+        s_tail->n = n;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
@@ -145,6 +241,20 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t tmem_base = *s_tmem;
     grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
 
+    // Item list of this CTA (see TailItems): items [0, rounds) are whole groups, the rest come from the table.
+    const int n_items = a.rounds + s_tail->n;
+    auto item_at = [&](int it, int& w, int& kb0, int& kb1) {
+        if (it < a.rounds) {
+            w = it * (int)gridDim.x + (int)blockIdx.x;
+            kb0 = 0;
+            kb1 = nkb;
+        } else {
+            w = s_tail->w[it - a.rounds];
+            kb0 = s_tail->kb0[it - a.rounds];
+            kb1 = s_tail->kb1[it - a.rounds];
+        }
+    };
+
     // Warpgroup 0 holds the two single-thread roles (and two idle warps) and gives registers away; the softmax
     // warpgroups take them: a softmax thread keeps a whole 128-key row of S in registers.
     if (warp < 4) {
@@ -152,19 +262,31 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
-            for (int t = 0; t < NQ; ++t) tma_load_4d(base + S::kQOff + t * kTileBytes, &tmap_q, q_full, 0, h, q0 + t * FQ, b);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int j = 0; j < nkb; ++j) {
-                if (!mbar_wait(k_empty(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
-                mbar_arrive_expect_tx(k_full(s), kTileBytes);
-                tma_load_4d(base + S::kKOff + s * kTileBytes, &tmap_k, k_full(s), 0, h, j * FK, b);
-                if (!mbar_wait(v_empty(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, 16 + s)) { ok = false; break; }
-                mbar_arrive_expect_tx(v_full(s), kTileBytes);
-                tma_load_4d(base + S::kVOff + s * kTileBytes, &tmap_v, v_full(s), 0, h, j * FK, b);
-                if (++s == kKVStages) { s = 0; ph ^= 1u; }
+#pragma unroll 1
+            for (int it = 0; it < n_items && ok; ++it) {
+                int w, kb0, kb1;
+                item_at(it, w, kb0, kb1);
+                const int bh = w / a.groups_per_head;
+                const int q0 = (w - bh * a.groups_per_head) * (FQ * NQ);
+                const int b = bh / a.H, h = bh - b * a.H;
+                // Q is single-buffered: the previous item's last Q K^T must have read it (that product is issued one unit
+                // early, so the reload overlaps the previous item's last softmax and write-out)
+                if (!mbar_wait(q_empty, ((uint32_t)it & 1u) ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, 32)) { ok = false; break; }
+                mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
+                for (int t = 0; t < NQ; ++t) tma_load_4d(base + S::kQOff + t * kTileBytes, &tmap_q, q_full, 0, h, q0 + t * FQ, b);
+#pragma unroll 1
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(k_empty(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
+                    mbar_arrive_expect_tx(k_full(s), kTileBytes);
+                    tma_load_4d(base + S::kKOff + s * kTileBytes, &tmap_k, k_full(s), 0, h, kb * FK, b);
+                    if (!mbar_wait(v_empty(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, 16 + s)) { ok = false; break; }
+                    mbar_arrive_expect_tx(v_full(s), kTileBytes);
+                    tma_load_4d(base + S::kVOff + s * kTileBytes, &tmap_v, v_full(s), 0, h, kb * FK, b);
+                    if (++s == kKVStages) { s = 0; ph ^= 1u; }
+                }
             }
             if (!ok) __nanosleep(20000);
         }
@@ -172,19 +294,22 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // ------------------------------------------------------------------ UMMA issuers: warp 1 for tile 0, warp 2 for tile 1
         // Each tile has its own issuer so that neither tile ever waits for the other one's turn. The whole warp runs the
         // code and one elected lane issues each instruction (descriptors and addresses stay warp-uniform).
-        // Per key block j the order follows the order in which the softmax group produces its events:
-        //   S_t free (the group has block j in registers)  ->  S_t(j+1) = Q_t K_{j+1}^T, issued while the group works on j
-        //   P_t(j) written                                  ->  O_t += P_t(j) V_j
+        // Per unit g (one key block of the current item) the order follows the softmax group's events:
+        //   S_t free (the group has unit g in registers)  ->  S_t(g+1) = Q_t K^T of the next unit, which may belong to
+        //                                                      the next item (other Q buffer), issued while the group works on g
+        //   P_t(g) written                                 ->  O_t (+)= P_t(g) V
         const int t = warp - 1;
         const uint32_t idesc_qk = make_idesc_f16(FQ, FK, !S16, false, false);
         const uint32_t idesc_pv = make_idesc_f16(FQ, 64, true, false, true);
         constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
-        const uint64_t qd = smem_desc(base + S::kQOff + t * kTileBytes, desc_hi);
+        const uint64_t qd0 = smem_desc(base + S::kQOff + t * kTileBytes, desc_hi);
         const uint64_t kd0 = smem_desc(base + S::kKOff, desc_hi);
         const uint64_t vd0 = smem_desc(base + S::kVOff, desc_hi);
-        const uint32_t dS = tmem_base + kColS + t * 128, dO = tmem_base + kColO + t * 64, aP = tmem_base + kColP + t * 64;
+        const uint32_t dS = tmem_base + t * kColTileS, dO = tmem_base + kColO + t * kColTileOP, aP = dO + kColP;
         auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
-        auto issue_qk = [&](int s) {
+        // S_t = Q_t K^T for one unit: Q buffer of item `it`, K in stage s; `last` = the item's last unit
+        auto issue_qk = [&](int s, bool last) {
+            const uint64_t qd = qd0;
             const uint64_t kd = kd0 + (uint64_t)(s * (kTileBytes >> 4));
             umma_ss_warp(dS, qd, kd, idesc_qk, 0u);
             umma_ss_warp(dS, qd + 2u, kd + 2u, idesc_qk, 1u);
@@ -192,42 +317,70 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             umma_ss_warp(dS, qd + 6u, kd + 6u, idesc_qk, 1u);
             umma_commit_warp(s_full(t));
             umma_commit_warp(k_empty(s));
+            if (last) umma_commit_warp(q_empty);  // the producer may load the next item's Q
         };
-        bool ok = all_ok(mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100));
+        int it = 0, kb = 0, kb1 = 0;
+        bool ok = n_items > 0;
+        if (ok) {
+            int w;
+            item_at(0, w, kb, kb1);
+        }
+        if (ok) ok = all_ok(mbar_wait(q_full, 0, s_abort, DEV_TIMEOUT_TMA_FULL, 100));
         if (ok) ok = all_ok(mbar_wait(k_full(0), 0, s_abort, DEV_TIMEOUT_TMA_FULL, 0));
         // Tile 1 starts once tile 0's group has its first block in registers: the two groups then run slightly out of
         // step, so that one group's load / maximum / store phases overlap the other group's exponentials (measured at
         // N = 6145: 668 -> 695 TFLOP/s for ff, 600 -> 667 for hh; longer offsets change nothing).
-        if (ok && t == 1 && nkb > 2) ok = all_ok(mbar_wait(s_free(0), 0, s_abort, DEV_TIMEOUT_TMEM_EMPTY, 50));
+        if (ok && t == 1 && (n_items > 1 || kb1 - kb > 2)) ok = all_ok(mbar_wait(s_free(0), 0, s_abort, DEV_TIMEOUT_TMEM_EMPTY, 50));
         if (ok) {
             tc_fence_after();
-            issue_qk(0);
+            issue_qk(0, kb + 1 == kb1);
         }
         int s = 0;
-        uint32_t ph = 0;
-        for (int j = 0; j < nkb && ok; ++j) {
+        uint32_t ph = 0, g = 0;
+        bool first = true;  // this unit starts an item: O_t is overwritten, not accumulated
+#pragma unroll 1
+        while (ok) {
             const int sn = (s + 1 == kKVStages) ? 0 : s + 1;
             const uint32_t phn = (s + 1 == kKVStages) ? ph ^ 1u : ph;
-            if (j + 1 < nkb) {
-                if (!all_ok(mbar_wait(s_free(t), (uint32_t)j & 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, t))) { ok = false; break; }
+            // the unit after this one
+            int nit = it, nkb_ = kb + 1, nkb1 = kb1;
+            bool nfirst = false, have_next = true;
+            if (nkb_ == kb1) {
+                nit = it + 1;
+                nfirst = true;
+                have_next = nit < n_items;
+                if (have_next) {
+                    int w;
+                    item_at(nit, w, nkb_, nkb1);
+                }
+            }
+            if (have_next) {
+                if (!all_ok(mbar_wait(s_free(t), g & 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, t))) { ok = false; break; }
+                if (nfirst && !all_ok(mbar_wait(q_full, (uint32_t)nit & 1u, s_abort, DEV_TIMEOUT_TMA_FULL, 101))) { ok = false; break; }
                 if (!all_ok(mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn))) { ok = false; break; }
                 tc_fence_after();
-                issue_qk(sn);
-                FBB_TRACE(2 + t, j + 1, 3);
+                issue_qk(sn, nkb_ + 1 == nkb1);
+                FBB_TRACE(2 + t, g + 1, 3);
             }
-            if (!all_ok(mbar_wait(p_ready(t), (uint32_t)j & 1u, s_abort, DEV_TIMEOUT_OTHER, 200 + t))) { ok = false; break; }
+            if (!all_ok(mbar_wait(p_ready(t), g & 1u, s_abort, DEV_TIMEOUT_OTHER, 200 + t))) { ok = false; break; }
             if (!all_ok(mbar_wait(v_full(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, 16 + s))) { ok = false; break; }
             tc_fence_after();
-            FBB_TRACE(2 + t, j, 1);
+            FBB_TRACE(2 + t, g, 1);
             const uint64_t vd = vd0 + (uint64_t)(s * (kTileBytes >> 4));
-            umma_ts_warp(dO, aP, vd, idesc_pv, j != 0 ? 1u : 0u);
+            umma_ts_warp(dO, aP, vd, idesc_pv, first ? 0u : 1u);
 #pragma unroll
             for (int k = 1; k < 8; ++k) umma_ts_warp(dO, aP + 8u * k, vd + 128u * k, idesc_pv, 1u);
             umma_commit_warp(pv_done(t));
             umma_commit_warp(v_empty(s));
-            FBB_TRACE(2 + t, j, 2);
+            FBB_TRACE(2 + t, g, 2);
+            if (!have_next) break;
+            it = nit;
+            kb = nkb_;
+            kb1 = nkb1;
+            first = nfirst;
             s = sn;
             ph = phn;
+            ++g;
         }
     }
     } else {
@@ -242,138 +395,196 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int t = (warp - 4) >> 3;
         const int lane_base = (u & 3) * 32 + (u >> 2) * 16;      // first tensor-memory lane (= row in the tile) of this warp
         const int cq = lane & 3;
-        const int rowA = q0 + t * FQ + lane_base + (lane >> 2);  // this thread's rows: rowA and rowA + 8
-        const uint32_t lane_addr = tmem_base + ((uint32_t)lane_base << 16);
-        const uint32_t tS = lane_addr + kColS + t * 128;
-        const uint32_t tO = lane_addr + kColO + t * 64;
-        const uint32_t tP = lane_addr + kColP + t * 64;
+        const uint32_t tS = tmem_base + ((uint32_t)lane_base << 16) + t * kColTileS;  // this warp's lanes of S_t
+        const uint32_t tO = tmem_base + ((uint32_t)lane_base << 16) + kColO + t * kColTileOP;  // ... of O_t; P_t is kColP further
         const float sl = a.scale_log2;
         float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;  // running maximum and (this thread's share of the) sum
         bool ok = true;
-        // A warp whose 16 rows all lie beyond N (the padding of the last tile) only keeps the barriers moving.
-        const bool warp_has_rows = q0 + t * FQ + lane_base < a.N;
+        uint32_t g = 0;  // units done: the phase of the per-tile barriers
 
-        for (int j = 0; j < nkb; ++j) {
-            if (u == 0) FBB_TRACE(t, j, 0);
-            if (!mbar_wait(s_full(t), j & 1, s_abort, DEV_TIMEOUT_TMEM_FULL, t)) { ok = false; break; }
-            tc_fence_after();
-            if (u == 0) FBB_TRACE(t, j, 1);
-            if (!warp_has_rows) {
-                // S_t(j+1) can be ready long before the other warps have written P_t(j): this warp's arrival for block
-                // j must not land in the phase of block j-1, so it watches that phase complete first.
-                if (j > 0 && !mbar_wait(p_ready(t), (uint32_t)(j - 1) & 1u, s_abort, DEV_TIMEOUT_OTHER, 210 + t)) { ok = false; break; }
+#pragma unroll 1
+        for (int it = 0; ok && it < n_items; ++it) {
+            int n;               // key blocks of this item still to do
+            bool to_end;         // the item runs to the group's last key block
+            bool warp_has_rows;  // a warp whose 16 rows all lie beyond N (padding of the last tile) only keeps the barriers moving
+            {
+                int w, kb0, kb1;
+                item_at(it, w, kb0, kb1);
+                n = kb1 - kb0;
+                to_end = kb1 == nkb;
+                warp_has_rows = (w % a.groups_per_head) * (FQ * NQ) + t * FQ + lane_base < a.N;
+            }
+            lA = lB = 0.f;
+            bool first = true;
+#pragma unroll 1
+            for (; n > 0; --n, ++g, first = false) {
+                if (u == 0) FBB_TRACE(t, g, 0);
+                if (!mbar_wait(s_full(t), g & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, t)) { ok = false; break; }
+                tc_fence_after();
+                if (u == 0) FBB_TRACE(t, g, 1);
+                if (!warp_has_rows) {
+                    // S_t(g+1) can be ready long before the other warps have written P_t(g): this warp's arrival for
+                    // unit g must not land in the phase of unit g-1, so it watches that phase complete first.
+                    if (g > 0 && !mbar_wait(p_ready(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_OTHER, 210 + t)) { ok = false; break; }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(s_free(t));
+                        mbar_arrive(p_ready(t));
+                    }
+                    continue;
+                }
+                uint32_t r[64];
+                tmem_ld_16x256b_x16(tS, r);
+                tmem_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(s_free(t));
-                    mbar_arrive(p_ready(t));
+                if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
+                float va[64];
+                if constexpr (!S16) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) va[i] = __uint_as_float(r[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) va[i] = __half2float(__ushort_as_half((unsigned short)(r[i] & 0xFFFFu)));
                 }
-                continue;
-            }
-            const int key0 = j * FK + 2 * cq;
-            const bool tail = j * FK + FK > a.N;
-            uint32_t r[64];
-            tmem_ld_16x256b_x16(tS, r);
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
-            float va[64];
-            if constexpr (!S16) {
+                if (to_end && n == 1 && (a.N & (FK - 1)) != 0) {  // the group's last key block is ragged: mask keys >= N
+                    const int key0 = (nkb - 1) * FK + 2 * cq;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) va[i] = __uint_as_float(r[i]);
-            } else {
+                    for (int k = 0; k < 16; ++k) {
+                        if (key0 + 8 * k >= a.N) va[4 * k] = va[4 * k + 2] = -INFINITY;
+                        if (key0 + 8 * k + 1 >= a.N) va[4 * k + 1] = va[4 * k + 3] = -INFINITY;
+                    }
+                }
+                float mxA = fmaxf(va[0], va[1]), mxB = fmaxf(va[2], va[3]);
 #pragma unroll
-                for (int i = 0; i < 64; ++i) va[i] = __half2float(__ushort_as_half((unsigned short)(r[i] & 0xFFFFu)));
-            }
-            if (tail) {
+                for (int k = 1; k < 16; ++k) {
+                    mxA = fmax3(mxA, va[4 * k], va[4 * k + 1]);
+                    mxB = fmax3(mxB, va[4 * k + 2], va[4 * k + 3]);
+                }
+                mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+                mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+                mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2)) * sl;
+                mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2)) * sl;
+                if (u == 0) FBB_TRACE(t, g, 2);
+                // ---- running maxima: raised only when this block exceeds them by more than 2^kLazyMax
+                if (first) {
+                    mA = mxA;
+                    mB = mxB;
+                } else if (__any_sync(0xffffffffu, mxA > mA + kLazyMax || mxB > mB + kLazyMax)) {
+                    // O_t is still being accumulated by the previous unit's P.V
+                    if (!mbar_wait(pv_done(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
+                    tc_fence_after();
+                    const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+                    const float cA = ex2_approx(mA - nA), cB = ex2_approx(mB - nB);
+                    uint32_t o[32];
+                    tmem_ld_16x256b_x8(tO, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA);
+                        o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA);
+                        o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB);
+                        o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB);
+                    }
+                    tmem_st_16x256b_x8(tO, o);
+                    lA *= cA;
+                    lB *= cB;
+                    mA = nA;
+                    mB = nB;
+                }
+                // ---- p = 2^(s*sl - m) in fp32; row sums in fp32; P as fp16 pairs back to tensor memory
+                const float2 sl2 = make_float2(sl, sl), nmA = make_float2(-mA, -mA), nmB = make_float2(-mB, -mB);
+                float2 accA = make_float2(0.f, 0.f), accB = make_float2(0.f, 0.f);
+                uint32_t pk[32];
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
-                    if (key0 + 8 * k >= a.N) va[4 * k] = va[4 * k + 2] = -INFINITY;
-                    if (key0 + 8 * k + 1 >= a.N) va[4 * k + 1] = va[4 * k + 3] = -INFINITY;
+                    const float2 xA = ffma2(make_float2(va[4 * k], va[4 * k + 1]), sl2, nmA);
+                    const float2 xB = ffma2(make_float2(va[4 * k + 2], va[4 * k + 3]), sl2, nmB);
+                    float2 pA, pB;
+                    if ((kEmuMask >> (k & 7)) & 1) {  // this key pair on the FMA pipes instead of the transcendental unit
+                        pA = exp2_emulated(xA);
+                        pB = exp2_emulated(xB);
+                    } else {
+                        pA = make_float2(ex2_approx(xA.x), ex2_approx(xA.y));
+                        pB = make_float2(ex2_approx(xB.x), ex2_approx(xB.y));
+                    }
+                    accA = fadd2(accA, pA);
+                    accB = fadd2(accB, pB);
+                    pk[2 * k] = pack_h2(pA.x, pA.y);
+                    pk[2 * k + 1] = pack_h2(pB.x, pB.y);
                 }
+                // P_t is read by the previous unit's P.V until that product has completed: waiting here, not before the
+                // exponentials, keeps the issue and run time of that product (~900 clocks) off the softmax warps' path
+                if (g > 0) {
+                    if (!mbar_wait(pv_done(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                tmem_st_16x128b_x16(tO + kColP, pk);
+                if (u == 0) FBB_TRACE(t, g, 3);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready(t));
+                if (u == 0) FBB_TRACE(t, g, 4);
+                lA += accA.x + accA.y;
+                lB += accB.x + accB.y;
             }
-            float mxA = fmaxf(va[0], va[1]), mxB = fmaxf(va[2], va[3]);
+            if (!ok || !warp_has_rows) continue;
+
+            // ---- end of an item: wait for its last P.V, then write the rows, or hand over / merge a split group
+            if (!mbar_wait(pv_done(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
+            tc_fence_after();
+            int w, kb0, kb1;
+            item_at(it, w, kb0, kb1);
+            uint32_t o[32];
+            tmem_ld_16x256b_x8(tO, o);
+            tmem_wait_ld();
+            const int wslot = t * 8 + u;
+            if (kb0 > 0) {
+                // Another CTA began this group: leave the partial result for it.
+                float* dst = a.ws_data + ((size_t)blockIdx.x * kSlotWarps + wslot) * (kSlotValues * 32) + lane;
 #pragma unroll
-            for (int k = 1; k < 16; ++k) {
-                mxA = fmax3(mxA, va[4 * k], va[4 * k + 1]);
-                mxB = fmax3(mxB, va[4 * k + 2], va[4 * k + 3]);
+                for (int i = 0; i < 32; ++i) dst[i * 32] = __uint_as_float(o[i]);
+                dst[32 * 32] = mA;
+                dst[33 * 32] = mB;
+                dst[34 * 32] = lA;
+                dst[35 * 32] = lB;
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release_gpu(a.ws_flags + (size_t)blockIdx.x * kSlotWarps + wslot, 1u);
+                continue;
             }
-            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
-            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
-            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2)) * sl;
-            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2)) * sl;
-            if (u == 0) FBB_TRACE(t, j, 2);
-            // O_t and P_t are still being read by P_t(j-1) . V until that product has completed (normally long ago)
-            if (j > 0) {
-                if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) { ok = false; break; }
-                tc_fence_after();
-            }
-            // ---- running maxima: raised only when this block exceeds them by more than 2^kLazyMax
-            if (j == 0) {
-                mA = mxA;
-                mB = mxB;
-            } else if (__any_sync(0xffffffffu, mxA > mA + kLazyMax || mxB > mB + kLazyMax)) {
-                const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+            if (kb1 != nkb) {
+                // The next CTA holds the rest of this group's keys (the first thing it did in its tail share).
+                unsigned* flag = a.ws_flags + (size_t)(blockIdx.x + 1u) * kSlotWarps + wslot;
+                if (!wait_slot_flag(flag, lane, s_abort, 300 + wslot)) { ok = false; break; }
+                const float* src = a.ws_data + ((size_t)(blockIdx.x + 1u) * kSlotWarps + wslot) * (kSlotValues * 32) + lane;
+                const float pmA = __ldcg(src + 32 * 32), pmB = __ldcg(src + 33 * 32);
+                const float nA = fmaxf(mA, pmA), nB = fmaxf(mB, pmB);
                 const float cA = ex2_approx(mA - nA), cB = ex2_approx(mB - nB);
-                uint32_t o[32];
-                tmem_ld_16x256b_x8(tO, o);
-                tmem_wait_ld();
+                const float dA = ex2_approx(pmA - nA), dB = ex2_approx(pmB - nB);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA);
-                    o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA);
-                    o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB);
-                    o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB);
+                    o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA + __ldcg(src + (4 * k) * 32) * dA);
+                    o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA + __ldcg(src + (4 * k + 1) * 32) * dA);
+                    o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB + __ldcg(src + (4 * k + 2) * 32) * dB);
+                    o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB + __ldcg(src + (4 * k + 3) * 32) * dB);
                 }
-                tmem_st_16x256b_x8(tO, o);
-                lA *= cA;
-                lB *= cB;
-                mA = nA;
-                mB = nB;
+                lA = lA * cA + __ldcg(src + 34 * 32) * dA;
+                lB = lB * cB + __ldcg(src + 35 * 32) * dB;
+                __syncwarp();
+                if (lane == 0) *flag = 0u;  // the slot is free for the next launch
             }
-            // ---- p = 2^(s*sl - m) in fp32; row sums in fp32; P as fp16 pairs back to tensor memory
-            const float2 sl2 = make_float2(sl, sl), nmA = make_float2(-mA, -mA), nmB = make_float2(-mB, -mB);
-            float2 accA = make_float2(0.f, 0.f), accB = make_float2(0.f, 0.f);
-            uint32_t pk[32];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const float2 xA = ffma2(make_float2(va[4 * k], va[4 * k + 1]), sl2, nmA);
-                const float2 xB = ffma2(make_float2(va[4 * k + 2], va[4 * k + 3]), sl2, nmB);
-                float2 pA, pB;
-                if ((kEmuMask >> (k & 7)) & 1) {  // this key pair on the FMA pipes instead of the transcendental unit
-                    pA = exp2_emulated(xA);
-                    pB = exp2_emulated(xB);
-                } else {
-                    pA = make_float2(ex2_approx(xA.x), ex2_approx(xA.y));
-                    pB = make_float2(ex2_approx(xB.x), ex2_approx(xB.y));
-                }
-                accA = fadd2(accA, pA);
-                accB = fadd2(accB, pB);
-                pk[2 * k] = pack_h2(pA.x, pA.y);
-                pk[2 * k + 1] = pack_h2(pB.x, pB.y);
-            }
-            tmem_st_16x128b_x16(tP, pk);
-            if (u == 0) FBB_TRACE(t, j, 3);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready(t));
-            if (u == 0) FBB_TRACE(t, j, 4);
-            lA += accA.x + accA.y;
-            lB += accB.x + accB.y;
-        }
-        if (ok && warp_has_rows && mbar_wait(pv_done(t), (uint32_t)(nkb - 1) & 1u, s_abort, DEV_TIMEOUT_TMEM_FULL, 8 + t)) {
-            tc_fence_after();
             // a row's sum is spread over the four threads that share it
             lA += __shfl_xor_sync(0xffffffffu, lA, 1);
             lB += __shfl_xor_sync(0xffffffffu, lB, 1);
             lA += __shfl_xor_sync(0xffffffffu, lA, 2);
             lB += __shfl_xor_sync(0xffffffffu, lB, 2);
             const float invA = 1.f / lA, invB = 1.f / lB;
-            uint32_t o[32];
-            tmem_ld_16x256b_x8(tO, o);
-            tmem_wait_ld();
+            const int bh = w / a.groups_per_head;
+            const int b = bh / a.H, h = bh - b * a.H;
+            const int rowA = (w - bh * a.groups_per_head) * (FQ * NQ) + t * FQ + lane_base + (lane >> 2);  // this thread's rows: rowA, rowA + 8
             __half* dstA = a.o + (int64_t)b * a.o_sb + (int64_t)rowA * a.o_sn + (int64_t)h * a.o_sh + 2 * cq;
             __half* dstB = dstA + 8 * a.o_sn;
 #pragma unroll
@@ -396,8 +607,8 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 template <int NQ, bool S16>
-static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashArgs& a, int B,
-                                cudaStream_t stream) {
+static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, FlashArgs a, int B, void* ws,
+                                int64_t ws_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -407,8 +618,34 @@ static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, co
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(flash64_umma_kernel): %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + FQ * NQ - 1) / (FQ * NQ)), (unsigned)(B * a.H), 1);
-    cudaError_t e = launch_pdl(kern, grid, dim3(128 + 256 * NQ), FlashSmem::kDynamic, stream, tq, tk, tv, a);
+    a.groups_per_head = (a.N + FQ * NQ - 1) / (FQ * NQ);
+    a.nkb = (a.N + FK - 1) / FK;
+    const int64_t groups = (int64_t)a.groups_per_head * B * a.H;
+    if (groups > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: too many query tiles (%lld)", (long long)groups);
+    a.ws_flags = nullptr;
+    a.ws_data = nullptr;
+    // One CTA per tile group, unless the groups do not fill the SMs evenly and the caller lent a workspace: then one
+    // persistent CTA per SM takes whole groups round-robin for all but the last full wave, and an equal share of the
+    // (group, key block) units of what is left (between one and two waves' worth, so every share is at least one group
+    // long and a group is split over at most two CTAs, which merge through the workspace).
+    const int sms = num_sms();
+    int64_t ctas = groups;
+    a.rounds = 1;
+    a.tail_units = 0;
+    const bool plain_only = getenv("FBB_FLASH_NO_SPLIT") != nullptr;  // tuning aid: always one CTA per group
+    if (groups > sms && groups % sms == 0 && !plain_only) {
+        ctas = sms;
+        a.rounds = (int)(groups / sms);
+    } else if (groups > sms && ws != nullptr && !plain_only) {
+        if (ws_bytes < flash64_workspace_bytes()) return fail(FBB_ERR_SHAPE, "flash64: workspace of %lld bytes, %lld needed", (long long)ws_bytes, (long long)flash64_workspace_bytes());
+        ctas = sms;
+        a.rounds = (int)(groups / sms) - 1;
+        a.tail_units = (groups - (int64_t)a.rounds * sms) * a.nkb;
+        a.ws_flags = reinterpret_cast<unsigned*>(ws);
+        a.ws_data = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + flag_region_bytes(sms));
+    }
+    if ((int64_t)a.rounds * a.nkb + 2 * (int64_t)a.nkb * 2 > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: too many key blocks per CTA");
+    cudaError_t e = launch_pdl(kern, dim3((unsigned)ctas), dim3(128 + 256 * NQ), FlashSmem::kDynamic, stream, tq, tk, tv, a);
     if (e != cudaSuccess) return fail((int)e, "flash64_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }
@@ -420,8 +657,22 @@ extern "C" int fbb_flash_trace_buffer(void* buf) {
 }
 #endif
 
+// Two query tiles per CTA once that still gives every SM a CTA; small inputs take one tile per CTA (the small-token path).
+static bool two_tiles_per_cta(int B, int N, int H) { return (int64_t)((N + 2 * FQ - 1) / (2 * FQ)) * B * H >= num_sms(); }
+
+int64_t flash64_workspace_bytes() { return (int64_t)(flag_region_bytes(num_sms()) + (size_t)num_sms() * kSlotFloats * sizeof(float)); }
+
+int64_t flash64_workspace_bytes_for(int B, int N, int H) {
+    if (B <= 0 || N <= 0 || H <= 0) return 0;
+    const int nq = two_tiles_per_cta(B, N, H) ? 2 : 1;
+    const int64_t groups = (int64_t)((N + FQ * nq - 1) / (FQ * nq)) * B * H;
+    const int sms = num_sms();
+    return (groups > sms && groups % sms != 0) ? flash64_workspace_bytes() : 0;
+}
+
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
-                   const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, cudaStream_t stream) {
+                   const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, void* ws, int64_t ws_bytes,
+                   cudaStream_t stream) {
     CUtensorMap tq, tk, tv;
     const uint64_t dims[4] = {64, (uint64_t)H, (uint64_t)N, (uint64_t)B};
     const uint32_t box[4] = {64, 1, 128, 1};
@@ -436,7 +687,7 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
         int rc = make_tmap_f16(maps[i], ptrs[i], 4, dims, st, box);
         if (rc != FBB_OK) return rc;
     }
-    FlashArgs a;
+    FlashArgs a = {};
     a.o = reinterpret_cast<__half*>(o);
     a.N = N;
     a.H = H;
@@ -444,12 +695,10 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
     a.o_sn = os[1];
     a.o_sh = os[2];
     a.scale_log2 = scale * 1.4426950408889634f;
-    // Small inputs: one 128-query tile per CTA so that more SMs get work (the small-token path).
-    const int64_t ctas2 = (int64_t)((N + 2 * FQ - 1) / (2 * FQ)) * B * H;
-    const bool two = ctas2 >= num_sms();
+    const bool two = two_tiles_per_cta(B, N, H);
     const bool s16 = variant == FBB_FLASH_HH;
-    if (two) return s16 ? launch_flash_variant<2, true>(tq, tk, tv, a, B, stream) : launch_flash_variant<2, false>(tq, tk, tv, a, B, stream);
-    return s16 ? launch_flash_variant<1, true>(tq, tk, tv, a, B, stream) : launch_flash_variant<1, false>(tq, tk, tv, a, B, stream);
+    if (two) return s16 ? launch_flash_variant<2, true>(tq, tk, tv, a, B, ws, ws_bytes, stream) : launch_flash_variant<2, false>(tq, tk, tv, a, B, ws, ws_bytes, stream);
+    return s16 ? launch_flash_variant<1, true>(tq, tk, tv, a, B, ws, ws_bytes, stream) : launch_flash_variant<1, false>(tq, tk, tv, a, B, ws, ws_bytes, stream);
 }
 
 }  // namespace fbb

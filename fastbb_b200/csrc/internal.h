@@ -72,7 +72,11 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
 // How many CTA pairs (clusters of two) of the linear kernel with `bn`-column tiles fit on the current device at once.
 int linear_max_pairs(int bn);
 
+// ws / ws_bytes: optional workspace (see fbb_flash64_f16_ws); null = one tile group per CTA, never split.
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
-                   const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, cudaStream_t stream);
+                   const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, void* ws, int64_t ws_bytes,
+                   cudaStream_t stream);
+// Workspace the split form needs on the current device for this shape; 0 when the shape is never split.
+int64_t flash64_workspace_bytes_for(int B, int N, int H);
 
 }  // namespace fbb

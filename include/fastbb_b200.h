@@ -6,12 +6,13 @@
  *
  * Conventions
  *  - every pointer is a device pointer in the caller's current CUDA context/device; nothing is allocated or freed by
- *    the library on any of these calls, and no call synchronises except fbb_device_status();
+ *    the library on any of these calls (the one kernel that wants scratch memory takes it from the caller, see
+ *    fbb_flash64_f16_ws), and no call synchronises except fbb_device_status();
  *  - `stream` is a cudaStream_t passed as void* (0 = legacy default stream); work is only enqueued;
  *  - all leading dimensions and strides are in ELEMENTS, not bytes;
  *  - return value: 0 = success, < 0 = argument rejected on the host before any launch (FBB_ERR_*), > 0 = cudaError_t;
  *    fbb_last_error() gives a thread-local message for the last non-zero status of the calling thread;
- *  - thread-compatible: no mutable state is shared between calls.
+ *  - thread-compatible: no mutable state is shared between calls, except a workspace the caller passes to both.
  */
 #ifndef FASTBB_B200_H_
 #define FASTBB_B200_H_
@@ -100,6 +101,23 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
 int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
                     int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
                     int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream);
+
+/* The same operator with a caller-owned workspace, which lets it balance the last, partly filled wave of query tiles:
+ * one persistent CTA per SM takes an equal share of the (query tile, key block) steps, and a tile whose keys end up
+ * split over two CTAs is merged through the workspace (unnormalised fp32 partial results + running maxima / sums).
+ * No counterpart in the reference (its kernels run one CTA per query tile); results are the same up to fp32 rounding
+ * of the merge.
+ *   fbb_flash64_workspace_bytes(B, N, H): bytes needed on the current device for this shape, 0 if it is never split.
+ *   workspace: device memory of at least that size, 16-byte aligned, ZEROED once by the caller before its first use;
+ *     it starts with one flag word per softmax warp and SM (64 bytes per SM), which every launch leaves zero again, so
+ *     it can be reused by any later call of any shape; the rest is overwritten freely. null (or a shape that needs
+ *     none) gives exactly fbb_flash64_f16. Calls that may overlap in time (different streams) need different workspaces.
+ *     If fbb_device_status() ever reports a failed wait, zero the workspace again before reusing it. */
+int64_t fbb_flash64_workspace_bytes(int B, int N, int H);
+int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                       int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                       int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace,
+                       int64_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -295,6 +295,43 @@ def test_flash_full_size_properties(variant, N):
     status_ok()
 
 
+@pytest.mark.parametrize("variant", ["ff", "hh"])
+@pytest.mark.parametrize("B,N,H", [(2, 2500, 11), (1, 4097, 12), (40, 300, 16), (1, 6145, 16), (3, 1370, 24)])
+def test_flash_split_form_matches_one_cta_per_group(oracle, variant, B, N, H):
+    """More query-tile groups than SMs and not a multiple of them: the persistent form splits some groups' keys over two
+    CTAs and merges them through the workspace. It must agree with the plain form (one CTA per group) up to rounding,
+    with the oracle where that is cheap, leave the workspace's flags cleared, and give the same answer when called again."""
+    from fastbb_b200 import _lib
+    from fastbb_b200.attention import attention
+    need = _lib.load().fbb_flash64_workspace_bytes(B, N, H)
+    if need == 0:
+        pytest.skip("this device's SM count divides the number of tile groups: nothing is split")
+    g = torch.Generator().manual_seed(B * 1000 + N * 10 + H)
+    qkv = torch.randn(B, N, 3, H, 64, generator=g).half()
+    qd, kd, vd = qkv.to(dev()).unbind(2)
+    ws = torch.zeros(need + 64, dtype=torch.uint8, device=dev())
+    plain = attention(qd, kd, vd, scale=0.125, variant=variant, workspace=False)
+    out, check = padded((B, N, H, 64))
+    split = attention(qd, kd, vd, scale=0.125, variant=variant, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    sms = torch.cuda.get_device_properties(dev()).multi_processor_count
+    assert int(ws[:64 * sms].count_nonzero()) == 0                        # the flag words (64 bytes per SM) are clear again
+    assert oracle.rel_l2(split.float().cpu(), plain.float().cpu()) < 3e-4
+    check()
+    again = attention(qd, kd, vd, scale=0.125, variant=variant, workspace=ws)
+    assert torch.equal(again, split)
+    default = attention(qd, kd, vd, scale=0.125, variant=variant)      # the module's own per-stream workspace
+    assert torch.equal(default, split)
+    if B * H * N * N <= 2 * 11 * 2500 * 2500:
+        q, k, v = qkv.unbind(2)
+        assert oracle.rel_l2(split.cpu().float(), oracle.attention(q, k, v, scale=0.125)) < (TOL_F16 if variant == "hh" else TOL_F32)
+    with pytest.raises(_lib.FastbbError):                                # a workspace that is too small is rejected, not ignored
+        _lib.check(_lib.load().fbb_flash64_f16_ws(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), B, N, H,
+                                                  *qd.stride()[:3], *kd.stride()[:3], *vd.stride()[:3], *out.stride()[:3],
+                                                  0.125, 0, ws.data_ptr(), 1024, None))
+    status_ok()
+
+
 def test_flash_rejects_what_the_kernel_does_not_cover():
     from fastbb_b200.attention import attention
     q = torch.zeros(1, 8, 2, 32, dtype=torch.float16, device=dev())
