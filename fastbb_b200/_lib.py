@@ -34,6 +34,7 @@ PROTOTYPES = {
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "fbb_flash64_f16_ws": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp, _i64, _vp]),
+    "fbb_flash64_f16_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
 }
 
 

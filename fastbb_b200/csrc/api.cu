@@ -179,4 +179,18 @@ int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B,
                               nullptr, 0, stream);
 }
 
+int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                           int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                           int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream) {
+    if (B < 0 || N < 0 || H <= 0) return fail(FBB_ERR_SHAPE, "flash64: bad B/N/H (%d, %d, %d)", B, N, H);
+    void* ws = nullptr;
+    int64_t ws_bytes = 0;
+    if (flash64_workspace_bytes_for(B, N, H) > 0) {  // only shapes that are split touch the workspace
+        const int rc = flash64_static_workspace(&ws, &ws_bytes, (cudaStream_t)stream);
+        if (rc != FBB_OK) return rc;
+    }
+    return fbb_flash64_f16_ws(q, k, v, o, B, N, H, q_sb, q_sn, q_sh, k_sb, k_sn, k_sh, v_sb, v_sn, v_sh, o_sb, o_sn, o_sh, scale, variant, ws,
+                              ws_bytes, stream);
+}
+
 }  // extern "C"

@@ -94,8 +94,14 @@ constexpr int kSlotWarps = 16;
 constexpr int kSlotValues = 36;
 constexpr size_t kSlotFloats = (size_t)kSlotWarps * kSlotValues * 32;
 constexpr size_t kFlagBytesPerCta = kSlotWarps * sizeof(unsigned);
-static size_t flag_region_bytes(int ctas) { return ((size_t)ctas * kFlagBytesPerCta + 255) & ~(size_t)255; }
+constexpr size_t flag_region_bytes(int ctas) { return ((size_t)ctas * kFlagBytesPerCta + 255) & ~(size_t)255; }
 int64_t flash64_workspace_bytes();
+
+// Built-in workspace of fbb_flash64_f16_static: room for the split form on a device of up to kStaticMaxSms SMs
+// (11.3 MiB; zero-initialised when the module is loaded, as the flag words must be).
+constexpr int kStaticMaxSms = 160;
+constexpr size_t kStaticWsBytes = flag_region_bytes(kStaticMaxSms) + (size_t)kStaticMaxSms * kSlotFloats * sizeof(float);
+static __device__ __align__(256) unsigned char g_flash_static_ws[kStaticWsBytes];
 
 #ifdef FBB_FLASH_TRACE
 // Development aid: per-iteration clock stamps of one softmax warp (CTA 0, lane 0 of warps 4 and 8) and of the UMMA
@@ -668,6 +674,31 @@ int64_t flash64_workspace_bytes_for(int B, int N, int H) {
     const int64_t groups = (int64_t)((N + FQ * nq - 1) / (FQ * nq)) * B * H;
     const int sms = num_sms();
     return (groups > sms && groups % sms != 0) ? flash64_workspace_bytes() : 0;
+}
+
+// Address and size of the built-in workspace on the current device; the address is looked up once per device. Enqueues
+// the clearing of its flag words on `stream` (calls share the array, and a launch that gave up a wait may have left some
+// raised). No memory is allocated.
+int flash64_static_workspace(void** ptr, int64_t* bytes, cudaStream_t stream) {
+    static void* addr[64] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail((int)e, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(FBB_ERR_SHAPE, "flash64 static workspace: device ordinal %d not supported", dev);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_flash_static_ws);
+        if (e != cudaSuccess || p == nullptr) return fail(e != cudaSuccess ? (int)e : FBB_ERR_DRIVER, "cudaGetSymbolAddress(static workspace): %s", cudaGetErrorString(e));
+        addr[dev] = p;
+    }
+    if (flash64_workspace_bytes() > (int64_t)kStaticWsBytes)
+        return fail(FBB_ERR_SHAPE, "flash64 static workspace holds %lld bytes (%d SMs), this device needs %lld", (long long)kStaticWsBytes,
+                    kStaticMaxSms, (long long)flash64_workspace_bytes());
+    e = cudaMemsetAsync(addr[dev], 0, flag_region_bytes(num_sms()), stream);
+    if (e != cudaSuccess) return fail((int)e, "cudaMemsetAsync(static workspace flags): %s", cudaGetErrorString(e));
+    *ptr = addr[dev];
+    *bytes = (int64_t)kStaticWsBytes;
+    return FBB_OK;
 }
 
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,

@@ -76,6 +76,8 @@ int linear_max_pairs(int bn);
 int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs,
                    const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int variant, void* ws, int64_t ws_bytes,
                    cudaStream_t stream);
+// The library's own (static device array) workspace for fbb_flash64_f16_static; clears its flag words on `stream`.
+int flash64_static_workspace(void** ptr, int64_t* bytes, cudaStream_t stream);
 // Workspace the split form needs on the current device for this shape; 0 when the shape is never split.
 int64_t flash64_workspace_bytes_for(int B, int N, int H);
 

@@ -119,6 +119,20 @@ int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int
                        int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace,
                        int64_t workspace_bytes, void* stream);
 
+/* fbb_flash64_f16_ws with the workspace built into the library: a file-scope device array of 11.3 MiB, enough for the
+ * split form on devices of up to 160 SMs (a device that needs more is rejected with FBB_ERR_SHAPE; shapes that are never
+ * split do not touch it). No counterpart in the reference. The call allocates and frees nothing: the array's address
+ * is looked up once per device (cudaGetSymbolAddress, with that device current) and kept.
+ *  - All calls on a device share the one array: two calls that may overlap in time (different streams) race on it and
+ *    give wrong results; use fbb_flash64_f16_ws with separate workspaces for that.
+ *  - The flag words at the start of the array must be zero when the kernel starts. They are when the library is loaded,
+ *    every completed launch leaves them so, and each call also enqueues a clear of them on `stream` ahead of the kernel,
+ *    so a launch that gave up a wait (see fbb_device_status) does not poison later calls.
+ *  - Make the first call on a device outside any stream capture: it is the one that resolves the array's address. */
+int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                           int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                           int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

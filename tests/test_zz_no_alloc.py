@@ -1,0 +1,53 @@
+"""fbb_flash64_f16_static: flash attention whose scratch memory is a device array inside the library.
+
+The file name sorts last on purpose: the entry point shares one array between all calls of the process, so it is
+exercised after everything else has run (and the tests also pass when this file is run alone).
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(fn_name, q, k, v, out, variant, *extra):
+    from fastbb_b200 import _lib
+    B, N, H, _ = q.shape
+    lib = _lib.load()
+    _lib.check(getattr(lib, fn_name)(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, N, H, *q.stride()[:3], *k.stride()[:3],
+                                     *v.stride()[:3], *out.stride()[:3], 0.125, _lib.FLASH_VARIANT[variant], *extra,
+                                     _lib.stream_ptr(q.device)))
+    return out
+
+
+@pytest.mark.parametrize("variant", ["fh", "hh"])
+@pytest.mark.parametrize("B,N,H", [(1, 6145, 16), (2, 2500, 11), (40, 300, 16), (1, 257, 6)])
+def test_static_workspace_matches_the_caller_workspace_entry_point(B, N, H, variant):
+    from fastbb_b200 import _lib
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(7 * B + N + H)
+    qkv = torch.randn(B, N, 3, H, 64, generator=g).half().to(dev)
+    q, k, v = qkv.unbind(2)
+    need = _lib.load().fbb_flash64_workspace_bytes(B, N, H)          # 0 for the small shape: nothing is split there
+    ws = torch.zeros(max(need, 16), dtype=torch.uint8, device=dev)
+    want = _call("fbb_flash64_f16_ws", q, k, v, torch.empty(B, N, H, 64, dtype=torch.float16, device=dev), variant,
+                 ws.data_ptr() if need else None, ws.numel() if need else 0)
+    plain = _call("fbb_flash64_f16", q, k, v, torch.empty_like(want), variant)
+    first = _call("fbb_flash64_f16_static", q, k, v, torch.empty_like(want), variant)
+    second = _call("fbb_flash64_f16_static", q, k, v, torch.empty_like(want), variant)   # straight after, same array
+    torch.cuda.synchronize()
+    assert torch.equal(first, want)              # same schedule, same arithmetic: bit-identical
+    assert torch.equal(second, want)
+    assert (first.float() - plain.float()).norm() / plain.float().norm() < 3e-4
+    assert _lib.device_status() == (0, 0, 0, 0)
+
+
+def test_static_workspace_entry_point_validates_like_the_others():
+    from fastbb_b200 import _lib
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.float16, device=dev)
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(_lib.load().fbb_flash64_f16_static(None, q.data_ptr(), q.data_ptr(), q.data_ptr(), 1, 8, 2, *q.stride()[:3], *q.stride()[:3],
+                                                      *q.stride()[:3], *q.stride()[:3], 0.125, 0, None))
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(_lib.load().fbb_flash64_f16_static(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 1, 8, 2, *q.stride()[:3],
+                                                      *q.stride()[:3], *q.stride()[:3], *q.stride()[:3], 0.125, 9, None))
