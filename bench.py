@@ -250,8 +250,9 @@ def run_ours(args, rank, local_rank, world):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one flash-attention launch at this workload, from the ncu capture
-# summarised in profiles/flash64_fh_N6145_H16.md (37.81 MB read, 0.01 MB written: the inputs once, the output stays in L2).
-ATTN_DRAM_TRAFFIC_BYTES = 37805824 + 11008
+# summarised in profiles/flash64_fh_N6145_H16.md (37.86 MB read, 0.64 MB written: the inputs once; the output and the
+# split groups' partial results stay in L2).
+ATTN_DRAM_TRAFFIC_BYTES = 37862912 + 637184
 
 
 def main():
