@@ -22,6 +22,17 @@ FLASH_VARIANT = {"ff": 0, "fh": 1, "hh": 2}
 
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
+class BlockDesc(ctypes.Structure):
+    """fbb_block_desc of include/fastbb_b200.h: weight pointers and shapes of one transformer block."""
+    _fields_ = ([(n, _vp) for n in ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "proj_w", "proj_b", "gamma1", "ln2_w", "ln2_b",
+                                    "fc1_w", "fc1_b", "fc2_w", "fc2_b", "gamma2")]
+                + [(n, _i32) for n in ("C", "heads", "hidden", "mlp", "acc_main", "acc_fc2", "flash_variant")]
+                + [(n, _f32) for n in ("eps1", "eps2", "scale")])
+
+
+MLP_GELU, MLP_SWIGLU = 0, 1
+_bdp = ctypes.POINTER(BlockDesc)
+
 # name -> (restype, argtypes); mirrors include/fastbb_b200.h one to one.
 PROTOTYPES = {
     "fbb_version": (_i32, []),
@@ -35,6 +46,9 @@ PROTOTYPES = {
     "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "fbb_flash64_f16_ws": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp, _i64, _vp]),
     "fbb_flash64_f16_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
+    "fbb_stack_scratch_bytes": (_i64, [_bdp, _i32, _i64]),
+    "fbb_stack_forward_f16": (_i32, [_bdp, _i32, _vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
+    "fbb_block_forward_f16": (_i32, [_bdp, _vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
 }
 
 
@@ -50,9 +64,9 @@ _LIB = None
 LAUNCHES = 0  # kernels enqueued through this module since import (each operator call is exactly one launch)
 
 
-def launched():
+def launched(n=1):
     global LAUNCHES
-    LAUNCHES += 1
+    LAUNCHES += n
 
 
 def load(path=None):

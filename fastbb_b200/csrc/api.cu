@@ -193,4 +193,20 @@ int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o,
                               ws_bytes, stream);
 }
 
+int64_t fbb_stack_scratch_bytes(const fbb_block_desc* blocks, int n_blocks, int64_t tokens) {
+    if (blocks == nullptr || n_blocks <= 0 || tokens <= 0) return 0;
+    return stack_scratch_bytes(blocks, n_blocks, tokens);
+}
+
+int fbb_stack_forward_f16(const fbb_block_desc* blocks, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes,
+                          void* workspace, int64_t workspace_bytes, void* stream) {
+    if (workspace != nullptr && (!aligned16(workspace) || workspace_bytes < 0)) return fail(FBB_ERR_ALIGN, "block: workspace must be 16-byte aligned");
+    return stack_forward(blocks, n_blocks, x, B, N, scratch, scratch_bytes, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int fbb_block_forward_f16(const fbb_block_desc* block, void* x, int B, int N, void* scratch, int64_t scratch_bytes, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+    return fbb_stack_forward_f16(block, 1, x, B, N, scratch, scratch_bytes, workspace, workspace_bytes, stream);
+}
+
 }  // extern "C"

@@ -3,4 +3,5 @@
 #include "layernorm.cu"
 #include "gemm.cu"
 #include "flash64.cu"
+#include "block.cu"
 #include "api.cu"

@@ -81,4 +81,9 @@ int flash64_static_workspace(void** ptr, int64_t* bytes, cudaStream_t stream);
 // Workspace the split form needs on the current device for this shape; 0 when the shape is never split.
 int64_t flash64_workspace_bytes_for(int B, int N, int H);
 
+// One FFI crossing per block / stack (block.cu): scratch needed for `tokens` tokens, and the launches themselves.
+int64_t stack_scratch_bytes(const fbb_block_desc* d, int n_blocks, int64_t tokens);
+int stack_forward(const fbb_block_desc* d, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes, void* ws,
+                  int64_t ws_bytes, cudaStream_t stream);
+
 }  // namespace fbb

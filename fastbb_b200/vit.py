@@ -14,12 +14,15 @@ seven launches of this package's own sm_100a kernels, with no torch fallback for
 small-input configuration). The process-global cuBLAS fp16-accumulation flag the reference flips around a run
 (fastbb/vit.py:27-34) is never touched: the accumulate mode is an argument of each GEMM.
 """
+import ctypes
 import math
+import os
 
 import torch
 import torch.nn.functional as F
 
-from .attention import attention
+from . import _lib
+from .attention import _workspace, attention
 from .gemm import linear
 from .layernorm import layer_norm
 
@@ -77,6 +80,88 @@ def run_block(block, x, attn_variant, gacc):
         return linear(h, m.fc2.weight, m.fc2.bias, res=x, gamma=g2, variant=v_fc2)
     h = linear(y, m.w12.weight, m.w12.bias, act="swiglu", variant=v_main)  # DINOv2 SwiGLU FFN (ViT-g)
     return linear(h, m.w3.weight, m.w3.bias, res=x, gamma=g2, variant=v_fc2)
+
+
+def _dev_f16(t, numel=None):
+    """Device pointer of an fp16 CUDA parameter the C block runner can read as is, None if absent; raises LookupError
+    for anything else (strided, other dtype): the caller then takes the per-operator path, which handles those."""
+    if t is None:
+        return None
+    if not (t.is_cuda and t.dtype == torch.float16 and t.is_contiguous() and t.data_ptr() % 16 == 0 and (numel is None or t.numel() == numel)):
+        raise LookupError
+    return t.data_ptr()
+
+
+def _ln_params(mod, C):
+    if not (isinstance(mod, torch.nn.LayerNorm) and tuple(mod.normalized_shape) == (C,)):
+        raise LookupError
+    return _dev_f16(mod.weight, C), _dev_f16(mod.bias, C), float(mod.eps)
+
+
+def _fill_block_desc(d, block, attn_variant, gacc):
+    """Weight pointers and shapes of `block` into the fbb_block_desc `d`; raises LookupError if the block is not of the
+    form fbb_stack_forward_f16 covers (LayerNorm norms, fp16 contiguous weights, erf-GELU or SwiGLU MLP, head dim 64)."""
+    a, m = block.attn, block.mlp
+    C = a.qkv.weight.shape[1]
+    H = a.num_heads
+    if C != H * HEAD_DIM or tuple(a.qkv.weight.shape) != (3 * C, C) or tuple(a.proj.weight.shape) != (C, C):
+        raise LookupError
+    v_main, v_fc2 = _gemm_variants(gacc)
+    d.ln1_w, d.ln1_b, d.eps1 = _ln_params(block.norm1, C)
+    d.ln2_w, d.ln2_b, d.eps2 = _ln_params(block.norm2, C)
+    d.qkv_w, d.qkv_b = _dev_f16(a.qkv.weight), _dev_f16(a.qkv.bias, 3 * C)
+    d.proj_w, d.proj_b = _dev_f16(a.proj.weight), _dev_f16(a.proj.bias, C)
+    d.gamma1, d.gamma2 = _dev_f16(_gamma(block, "ls1"), C), _dev_f16(_gamma(block, "ls2"), C)
+    if hasattr(m, "fc1"):
+        if not _is_erf_gelu(getattr(m, "act", None)):
+            raise LookupError
+        fc1, fc2, hidden, d.mlp = m.fc1, m.fc2, m.fc1.weight.shape[0], _lib.MLP_GELU
+        rows1 = hidden
+    else:
+        fc1, fc2, hidden, d.mlp = m.w12, m.w3, m.w12.weight.shape[0] // 2, _lib.MLP_SWIGLU
+        rows1 = 2 * hidden
+    if tuple(fc1.weight.shape) != (rows1, C) or tuple(fc2.weight.shape) != (C, hidden) or hidden % 8:
+        raise LookupError
+    d.fc1_w, d.fc1_b = _dev_f16(fc1.weight), _dev_f16(fc1.bias, rows1)
+    d.fc2_w, d.fc2_b = _dev_f16(fc2.weight), _dev_f16(fc2.bias, C)
+    d.C, d.heads, d.hidden = C, H, hidden
+    d.acc_main, d.acc_fc2 = _ACC[v_main], _ACC[v_fc2]
+    d.flash_variant = _lib.FLASH_VARIANT["ff" if attn_variant == "sdpa" else attn_variant]
+    scale = getattr(a, "scale", None)
+    d.scale = float(HEAD_DIM ** -0.5 if scale is None else scale)
+    if not d.scale > 0:
+        raise LookupError
+
+
+_ACC = {"f32": _lib.ACC_F32, "h": _lib.ACC_F16}
+
+
+def run_stack(blocks, x, attn_variant, gacc):
+    """blocks[...] applied IN PLACE to x [B, N, C] (fp16, contiguous, CUDA) through ONE call of the C stack runner
+    (fbb_stack_forward_f16: 7 launches per block, the same kernels in the same order as run_block). Returns False
+    without touching x if some block is outside what the runner covers; the caller then uses run_block."""
+    n = len(blocks)
+    descs = (_lib.BlockDesc * n)()
+    try:
+        for d, b in zip(descs, blocks):
+            _fill_block_desc(d, b, attn_variant, gacc)
+    except (LookupError, AttributeError):
+        return False
+    if not (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() == 3 and x.shape[2] == descs[0].C):
+        return False
+    B, N, _ = x.shape
+    if B == 0 or N == 0 or n == 0:
+        return True
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        scratch = torch.empty(lib.fbb_stack_scratch_bytes(descs, n, B * N), device=x.device, dtype=torch.uint8)
+        need = lib.fbb_flash64_workspace_bytes(B, N, descs[0].heads)
+        ws = _workspace(x.device, need) if need > 0 else None
+        _lib.check(lib.fbb_stack_forward_f16(descs, n, x.data_ptr(), B, N, scratch.data_ptr(), scratch.numel(),
+                                             ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                             _lib.stream_ptr(x.device)))
+    _lib.launched(7 * n)
+    return True
 
 
 def _param_version(parameters):
@@ -224,12 +309,18 @@ class FastViT:
         last = max(layers)
         with torch.autocast("cuda", enabled=False):
             t = self.tokens(x).contiguous()
-            for i, b in enumerate(self.blocks):
-                t = run_block(b, t, self.attn, self.gacc)
-                if i in layers:
-                    out.append(_norm(self.vit.norm, t) if norm else t.clone())
-                if i >= last:
-                    break
+            # One C call per run of blocks between two selected layers (t is this function's own buffer, updated in
+            # place); blocks the C runner does not cover, or FBB_NO_RUNNER=1, take the per-operator path.
+            use_runner = os.environ.get("FBB_NO_RUNNER") != "1"
+            i = 0
+            while i <= last:
+                j = min([l for l in layers if l >= i])  # next selected layer
+                if not (use_runner and run_stack(self.blocks[i:j + 1], t, self.attn, self.gacc)):
+                    use_runner = False
+                    for b in self.blocks[i:j + 1]:
+                        t = run_block(b, t, self.attn, self.gacc)
+                out.append(_norm(self.vit.norm, t) if norm else t.clone())
+                i = j + 1
         return out
 
     def run_graphed(self, x, layers, norm=True):

@@ -133,6 +133,45 @@ int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o,
                            int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
                            int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream);
 
+/* ---- one FFI crossing per transformer block or per run of blocks -------------------------------------------------------
+ * Replaces FastViT.block / block_chunked and the loop over blocks in FastViT.run (fastbb/vit.py:108-172, 175-187), which
+ * cross from Python into torch / ctypes ten to eleven times per block. The same seven kernels are enqueued in the same
+ * order as through the per-operator entry points, so the results are bit-identical to those.
+ * All weights fp16 in nn.Linear layout, contiguous (leading dimension = row length); null bias / LayerNorm affine /
+ * LayerScale pointers mean "absent". */
+enum fbb_mlp_kind {
+    FBB_MLP_GELU = 0,   /* fc1 [hidden, C] + erf-GELU, fc2 [C, hidden]            (fastbb/vit.py:121-131) */
+    FBB_MLP_SWIGLU = 1  /* fc1 = w12 [2*hidden, C], silu(x1)*x2, fc2 = w3 [C, hidden] (fastbb/vit.py:139-143) */
+};
+
+typedef struct fbb_block_desc {
+    const void *ln1_w, *ln1_b;     /* [C] */
+    const void *qkv_w, *qkv_b;     /* [3C, C], [3C] */
+    const void *proj_w, *proj_b;   /* [C, C], [C] */
+    const void *gamma1;            /* LayerScale of the attention branch [C] */
+    const void *ln2_w, *ln2_b;     /* [C] */
+    const void *fc1_w, *fc1_b;     /* see fbb_mlp_kind */
+    const void *fc2_w, *fc2_b;
+    const void *gamma2;            /* LayerScale of the MLP branch [C] */
+    int C, heads, hidden;          /* C = heads * 64; hidden = columns of the MLP's hidden activation */
+    int mlp;                       /* fbb_mlp_kind */
+    int acc_main, acc_fc2;         /* fbb_accumulate of qkv / proj / fc1, and of fc2 (the reference's g2 keeps fc2 in fp32) */
+    int flash_variant;             /* fbb_flash_variant */
+    float eps1, eps2;              /* LayerNorm epsilons */
+    float scale;                   /* attention scale, > 0 */
+} fbb_block_desc;
+
+/* Bytes of scratch (LayerNorm output, packed qkv, attention output, MLP hidden) the blocks need for `tokens` = B*N tokens. */
+int64_t fbb_stack_scratch_bytes(const fbb_block_desc* blocks, int n_blocks, int64_t tokens);
+
+/* x [B, N, C] fp16 contiguous is updated IN PLACE by n_blocks blocks (the residual epilogues write over their residual
+ * input). scratch: 256-byte aligned device memory of at least fbb_stack_scratch_bytes(); workspace: optional, as for
+ * fbb_flash64_f16_ws. Nothing is allocated; 7 * n_blocks kernels are enqueued on `stream`. */
+int fbb_stack_forward_f16(const fbb_block_desc* blocks, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes,
+                          void* workspace, int64_t workspace_bytes, void* stream);
+int fbb_block_forward_f16(const fbb_block_desc* block, void* x, int B, int N, void* scratch, int64_t scratch_bytes, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

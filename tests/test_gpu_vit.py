@@ -207,3 +207,54 @@ def test_host_pipeline_matches_direct_calls(oracle):
     assert pipe.h2d_bytes == 2 * 3 * 224 * 224 * 4 and pipe.d2h_bytes == 2 * 2 * (256 + 1) * 384 * 2
     with pytest.raises(ValueError):
         pipe.result(tickets[0])
+
+
+@pytest.mark.parametrize("arch,hw,spec", [("vits14", 224, "fh-g0"), ("vits14", 238, "hh-g1"), ("vits14", 224, "fh-g2"),
+                                          ("vitg14", 224, "hh-g1")])
+def test_c_stack_runner_equals_per_operator_path(oracle, arch, hw, spec, monkeypatch):
+    """FastViT.run hands each run of blocks between selected layers to ONE C call (fbb_stack_forward_f16). It launches
+    the same kernels in the same order as the per-operator path (FBB_NO_RUNNER=1), so the outputs must be identical
+    bit for bit, and both count 7 launches per block."""
+    from fastbb_b200 import _lib
+    depth = 4 if arch == "vitg14" else None
+    params, fast = _fast_model(oracle, arch, spec, **({"depth": depth} if depth else {}))
+    x = oracle.make_image(2, hw, hw, seed=3).to("cuda:0")
+    n = [1, 3] if depth else [2, 5, 11]
+    before = _lib.LAUNCHES
+    a = fast.get_intermediate_layers(x, n=n, return_class_token=True, norm=False)
+    launches_runner = _lib.LAUNCHES - before
+    monkeypatch.setenv("FBB_NO_RUNNER", "1")
+    before = _lib.LAUNCHES
+    b = fast.get_intermediate_layers(x, n=n, return_class_token=True, norm=False)
+    assert _lib.LAUNCHES - before == launches_runner
+    for (pa, ca), (pb, cb) in zip(a, b):
+        assert torch.equal(pa, pb) and torch.equal(ca, cb)
+    assert _lib.device_status() == (0, 0, 0, 0)
+
+
+def test_c_block_runner_direct_call_and_validation(oracle):
+    """fbb_block_forward_f16 through ctypes on one block: equals run_block, updates x in place, rejects a scratch that is
+    too small, a head count that does not match C, and a null weight."""
+    import ctypes
+    from fastbb_b200 import _lib, vit as V
+    params, fast = _fast_model(oracle, "vits14", "fh-g0")
+    blk = fast.blocks[0]
+    x = (0.5 * torch.randn(1, 300, 384, generator=torch.Generator().manual_seed(1))).half().to("cuda:0")
+    want = V.run_block(blk, x, "fh", False)
+    d = _lib.BlockDesc()
+    V._fill_block_desc(d, blk, "fh", False)
+    lib = _lib.load()
+    need = lib.fbb_stack_scratch_bytes(ctypes.byref(d), 1, 300)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda:0")
+    got = x.clone()
+    _lib.check(lib.fbb_block_forward_f16(ctypes.byref(d), got.data_ptr(), 1, 300, scratch.data_ptr(), need, None, 0, None))
+    assert torch.equal(got, want)
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(lib.fbb_block_forward_f16(ctypes.byref(d), got.data_ptr(), 1, 300, scratch.data_ptr(), need - 256, None, 0, None))
+    d.heads = 5
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(lib.fbb_block_forward_f16(ctypes.byref(d), got.data_ptr(), 1, 300, scratch.data_ptr(), need, None, 0, None))
+    d.heads, d.fc2_w = 6, None
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(lib.fbb_block_forward_f16(ctypes.byref(d), got.data_ptr(), 1, 300, scratch.data_ptr(), need, None, 0, None))
+    assert _lib.device_status() == (0, 0, 0, 0)
