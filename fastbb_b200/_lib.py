@@ -5,7 +5,13 @@ Python/PyTorch and crosses one thin FFI boundary per operator. Differences: the 
 entry point per operator instead of a kernel-name + signature-string table; a non-zero status becomes a Python
 exception; nothing is cached per device in Python, so several GPUs can be used from one process.
 There is no CPU or PyTorch fallback: if the library is missing, importing an operator raises.
+
+Attention on its own: `attention.py` + this file + `libfastbb_flash64.so` (`python -m fastbb_b200.build --flash-only`) are
+all a project needs that vendors only the attention API, as several forks do with the reference's
+attention.py + kernels.py. When the full library is absent, load() falls back to that one and sets up only the
+entry points it exports.
 """
+import contextlib
 import ctypes
 import os
 
@@ -13,6 +19,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfastbb_b200.so")
+FLASH_LIB_PATH = os.path.join(_HERE, "libfastbb_flash64.so")   # attention kernel and its entry points only
 
 FBB_OK = 0
 DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
@@ -21,6 +28,12 @@ ACC_F32, ACC_F16 = 0, 1
 FLASH_VARIANT = {"ff": 0, "fh": 1, "hh": 2}
 
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+
+def on(device):
+    """Context manager that makes `device` current for the enclosed C calls (a no-op when it already is)."""
+    return torch.cuda.device(device) if device.index != torch.cuda.current_device() else contextlib.nullcontext()
+
 
 class BlockDesc(ctypes.Structure):
     """fbb_block_desc of include/fastbb_b200.h: weight pointers and shapes of one transformer block."""
@@ -69,16 +82,25 @@ def launched(n=1):
     LAUNCHES += n
 
 
+# what libfastbb_flash64.so exports (the other prototypes are skipped when that library is the one loaded)
+FLASH_ONLY_SYMBOLS = ("fbb_version", "fbb_status_string", "fbb_last_error", "fbb_device_status", "fbb_flash64_f16",
+                      "fbb_flash64_workspace_bytes", "fbb_flash64_f16_ws", "fbb_flash64_f16_static")
+
+
 def load(path=None):
-    """Load (once) and return the ctypes handle with every prototype set. Raises OSError if the library is not built."""
+    """Load (once) and return the ctypes handle with every prototype set. Without `path`: the full library, or, if only
+    the attention-only library has been built, that one. Raises OSError if neither exists."""
     global _LIB
     if _LIB is None or path is not None:
-        p = path or LIB_PATH
+        p = path or (LIB_PATH if os.path.exists(LIB_PATH) or not os.path.exists(FLASH_LIB_PATH) else FLASH_LIB_PATH)
         if not os.path.exists(p):
             raise OSError(f"{p} not found: build it with `python -m fastbb_b200.build` (needs nvcc with sm_100a support); "
                           "there is no fallback path")
         lib = ctypes.CDLL(p)
+        lib.flash_only = not hasattr(lib, "fbb_linear_f16")
         for name, (res, args) in PROTOTYPES.items():
+            if lib.flash_only and name not in FLASH_ONLY_SYMBOLS:
+                continue
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
         if path is not None:

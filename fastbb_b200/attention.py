@@ -18,7 +18,6 @@ stream) for that and hands it to fbb_flash64_f16_ws; `workspace=False` selects t
 import torch
 
 from . import _lib
-from .layernorm import _on
 
 
 def _ok(t):
@@ -56,7 +55,7 @@ def attention(q, k, v, scale=None, out=None, variant="hh", rows=None, workspace=
         out = torch.empty((B, N, H, D), device=q.device, dtype=q.dtype)
     if B == 0 or N == 0 or H == 0:
         return out
-    with _on(q.device):
+    with _lib.on(q.device):
         lib = _lib.load()
         ws_ptr, ws_bytes = None, 0
         if workspace is not False:

@@ -112,6 +112,7 @@ int fbb_device_status(unsigned int out[4]) {
     return FBB_OK;
 }
 
+#ifndef FBB_FLASH_ONLY  // the attention-only build leaves out the linear, LayerNorm and block entry points
 int fbb_linear_max_cta_pairs(int tile_columns) {
     if (tile_columns != 128 && tile_columns != 256) return fail(FBB_ERR_ENUM, "tile_columns must be 128 or 256");
     return linear_max_pairs(tile_columns);
@@ -150,6 +151,8 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
         return fail(FBB_ERR_ALIGN, "linear: A, W, C, res must be 16-byte aligned with leading dimensions %% 8 == 0");
     return launch_linear(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, (cudaStream_t)stream);
 }
+
+#endif  // FBB_FLASH_ONLY
 
 int64_t fbb_flash64_workspace_bytes(int B, int N, int H) { return flash64_workspace_bytes_for(B, N, H); }
 
@@ -193,6 +196,7 @@ int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o,
                               ws_bytes, stream);
 }
 
+#ifndef FBB_FLASH_ONLY
 int64_t fbb_stack_scratch_bytes(const fbb_block_desc* blocks, int n_blocks, int64_t tokens) {
     if (blocks == nullptr || n_blocks <= 0 || tokens <= 0) return 0;
     return stack_scratch_bytes(blocks, n_blocks, tokens);
@@ -208,5 +212,7 @@ int fbb_block_forward_f16(const fbb_block_desc* block, void* x, int B, int N, vo
                           int64_t workspace_bytes, void* stream) {
     return fbb_stack_forward_f16(block, 1, x, B, N, scratch, scratch_bytes, workspace, workspace_bytes, stream);
 }
+
+#endif  // FBB_FLASH_ONLY
 
 }  // extern "C"

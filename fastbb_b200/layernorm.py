@@ -3,15 +3,12 @@
 Stands in for the `b.norm1(x)`, `b.norm2(x)` and `vit.norm(t)` module calls of the reference's block
 (fastbb/vit.py:114,126,130,139,159,166,170,184,241), which run aten's native_layer_norm.
 """
-import contextlib
-
 import torch
 
 from . import _lib
 
 
-def _on(device):
-    return torch.cuda.device(device) if device.index != torch.cuda.current_device() else contextlib.nullcontext()
+_on = _lib.on
 
 
 def layer_norm(x, weight=None, bias=None, eps=1e-6, out=None):

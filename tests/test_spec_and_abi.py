@@ -60,6 +60,18 @@ def test_library_exports_every_declared_symbol():
     assert lib.fbb_version() == 100
 
 
+def test_attention_only_library_exports_the_attention_subset():
+    """libfastbb_flash64.so (python -m fastbb_b200.build --flash-only) is what a project that vendors only attention.py
+    and _lib.py loads: the attention entry points and the status calls, nothing else."""
+    from fastbb_b200 import _lib, build
+    lib = _lib.load(build.build(flash_only=True))
+    assert lib.flash_only and lib.fbb_version() == 100
+    for n in _declared_functions():
+        assert hasattr(lib, n) == (n in _lib.FLASH_ONLY_SYMBOLS), n
+    q = ctypes.c_void_p(256)
+    assert lib.fbb_flash64_f16(q, q, q, q, 1, 8, 2, 1024, 128, 64, 1024, 128, 64, 1024, 128, 64, 1024, 128, 64, 0.125, 7, None) == -4
+
+
 def test_missing_library_fails_loudly(tmp_path):
     from fastbb_b200 import _lib
     with pytest.raises(OSError, match="no fallback"):

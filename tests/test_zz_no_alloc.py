@@ -51,3 +51,18 @@ def test_static_workspace_entry_point_validates_like_the_others():
     with pytest.raises(_lib.FastbbError):
         _lib.check(_lib.load().fbb_flash64_f16_static(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 1, 8, 2, *q.stride()[:3],
                                                       *q.stride()[:3], *q.stride()[:3], *q.stride()[:3], 0.125, 9, None))
+
+
+def test_attention_only_library_gives_the_same_attention():
+    """The attention-only build (libfastbb_flash64.so) holds the same kernel: same bits as the full library."""
+    from fastbb_b200 import _lib, build
+    flash = _lib.load(build.build(flash_only=True))
+    dev = torch.device("cuda", 0)
+    qkv = torch.randn(1, 1370, 3, 16, 64, generator=torch.Generator().manual_seed(9)).half().to(dev)
+    q, k, v = qkv.unbind(2)
+    want = _call("fbb_flash64_f16", q, k, v, torch.empty(1, 1370, 16, 64, dtype=torch.float16, device=dev), "fh")
+    got = torch.empty_like(want)
+    _lib.check(flash.fbb_flash64_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), got.data_ptr(), 1, 1370, 16, *q.stride()[:3], *k.stride()[:3],
+                                     *v.stride()[:3], *got.stride()[:3], 0.125, _lib.FLASH_VARIANT["fh"], _lib.stream_ptr(dev)))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
