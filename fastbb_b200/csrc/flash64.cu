@@ -67,7 +67,6 @@ constexpr unsigned kEmuMask = FBB_EMU_MASK;  // e.g. 0x88: pairs 3 and 7 of 8 (2
 constexpr int kRegsCtl = 40, kRegsSoftmax = 104;
 static_assert(128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96, "setmaxnreg split exceeds the CTA's register pool");
 
-// tensor-memory columns
 // tensor-memory columns of tile t: S_t (128 columns) at t * kColTileS, O_t (fp32, 64 columns) at kColO + t * kColTileOP,
 // P_t (fp16 pairs, 64 columns) kColP after O_t
 constexpr uint32_t kColTileS = 128, kColO = 256, kColTileOP = 64, kColP = 128;
@@ -82,8 +81,7 @@ struct FlashSmem {
     static constexpr int kTailOff = kBarOff + kNumBars * 8 + 16;    // TailItems (40 bytes)
     static constexpr int kBytes = kTailOff + 48;
     // No slack for aligning by hand (the array is declared 1024-byte aligned): 160.4 KB keeps the CTA inside the 164 KB
-    // shared-memory configuration, which leaves 92 KB of L1 for the softmax warps' register spills. With 32 KB more
-    // (a second Q buffer was tried) the SM falls to 28 KB of L1 and the whole kernel runs 13 % slower.
+    // shared-memory configuration, which leaves the rest of the SM's 256 KB to L1 (the softmax warps spill a few registers).
     static constexpr int kDynamic = kBytes;
 };
 
