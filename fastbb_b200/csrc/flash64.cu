@@ -45,6 +45,8 @@
 // catches up. CTAs that live for one group (<= ~130 units) mostly keep it; the persistent form loses part of what it
 // gains from the removed wave this way. Forcing strict turns with an extra barrier pair costs more than it saves (3100).
 #include "common.cuh"
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace fbb {
@@ -678,7 +680,7 @@ static bool two_tiles_per_cta(int B, int N, int H) { return (int64_t)((N + 2 * F
 int64_t flash64_workspace_bytes() { return (int64_t)(flag_region_bytes(num_sms()) + (size_t)num_sms() * kSlotFloats * sizeof(float)); }
 
 int64_t flash64_workspace_bytes_for(int B, int N, int H) {
-    if (B <= 0 || N <= 0 || H <= 0) return 0;
+    if (B <= 0 || N <= 0 || H <= 0 || getenv("FBB_FLASH_NO_SPLIT") != nullptr) return 0;
     const int nq = two_tiles_per_cta(B, N, H) ? 2 : 1;
     const int64_t groups = (int64_t)((N + FQ * nq - 1) / (FQ * nq)) * B * H;
     const int sms = num_sms();
