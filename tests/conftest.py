@@ -16,6 +16,18 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
 
 
+def pytest_sessionstart(session):
+    """Build the C-ABI libraries when they are missing or older than their sources (they are build artefacts, not
+    tracked files). Without nvcc nothing is built and the tests that need the library fail with its own message."""
+    import shutil
+    from fastbb_b200 import build
+    if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+        for flash_only in (False, True):
+            out = build.FLASH_OUT if flash_only else build.OUT
+            if not build.up_to_date(out):
+                build.build(flash_only=flash_only)
+
+
 def pytest_collection_modifyitems(config, items):
     if torch.cuda.is_available():
         return
