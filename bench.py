@@ -211,6 +211,9 @@ def run_ours(args, rank, local_rank, world):
         return o
     fast.graphs = False
     vit_mod.attention = timed_attention
+    # the per-operator host path (same kernels, same order as the C stack runner) so that each launch can be bracketed
+    runner_env = os.environ.get("FBB_NO_RUNNER")
+    os.environ["FBB_NO_RUNNER"] = "1"
     try:
         for _ in range(args.steps):
             step(x_dev)
@@ -218,6 +221,11 @@ def run_ours(args, rank, local_rank, world):
     finally:
         vit_mod.attention = real_attention
         fast.graphs = graphs
+        if runner_env is None:
+            del os.environ["FBB_NO_RUNNER"]
+        else:
+            os.environ["FBB_NO_RUNNER"] = runner_env
+    assert len(marks) == DEPTH * args.steps, "the instrumented pass did not see every attention launch"
     attn_ms = [s.elapsed_time(e) for s, e in marks]
     attn_mean_ms = sum(attn_ms) / len(attn_ms)
     peaks = measured_peaks()

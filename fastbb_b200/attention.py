@@ -5,7 +5,8 @@ Same call signature as the reference's fastbb/attention.py:31 `attention`:
 attention(q, k, v, scale=None, out=None, variant="hh")
     q, k, v: [B, N, H, 64] fp16 views (d contiguous, other strides multiples of 8 elements; e.g. the unbound packed qkv
     GEMM output [B, N, 3, H, 64]); returns O as [B, N, H, 64] (contiguous -> .view(B, N, H*64), no transpose).
-variant: "hh" fp16-accumulate QK^T and PV (fastest), "fh" fp32 QK^T + fp16 PV, "ff" fp32 both.
+variant: the reference's "hh" / "fh" / "ff" (accumulate types of QK^T and PV in its kernels) are all accepted; on B200
+both products accumulate in fp32 for every variant (an f16 tensor-memory accumulator is no faster and costs a conversion).
 Small inputs run the same kernel with one 128-query tile per CTA instead of the reference's SDPA fallback
 (fastbb/vit.py:146-150); anything the kernel does not cover (other head dims, dtypes, strides, CPU tensors,
 scale <= 0) raises instead of falling back to torch (fastbb/attention.py:38-48).

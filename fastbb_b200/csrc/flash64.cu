@@ -13,8 +13,8 @@
 //     O (fp32), the running maxima and sums in its workspace slot and raises the slot's per-warp flags;
 //   - the CTA that began that group (always the last item of its share, so it needs the slot late) merges the slot into
 //     its own accumulators, clears the flags and writes the rows.
-// With 400 groups on 148 SMs (ViT-L/14 at 896x1344) this replaces 3 waves by 2.7: fp16-S variant 243 -> 215 us per
-// launch; the fp32-S variant stays at ~201 us because the two tiles of a long-lived CTA drift into step (see below).
+// With 400 groups on 148 SMs (ViT-L/14 at 896x1344) this replaces 3 waves by 2.7; part of the gain is lost because the
+// two tiles of a long-lived CTA drift into step (see below): 2.5 % on whole-model time.
 //
 //   warp 0          TMA producer: the Q tiles of each item, then K_j and V_j into a ring of stages (128-byte swizzle, zero fill)
 //   warps 1, 2      UMMA issuers, one per tile: S_t = Q_t K_j^T (both K-major, 4 x K16) into tensor memory, issued as
@@ -33,10 +33,13 @@
 //                   Four softmax warps share each SM sub-partition and cover one another's waits (measured against
 //                   one-thread-per-row groups of four warps: 740 -> 849 TFLOP/s at N = 16385).
 // With NQ = 2 the two groups alternate on the tensor core (S of one tile is computed while the other tile is in its
-// softmax). Variants (fastbb/attention.py:5-7) select the accumulate type of S: ff / fh -> fp32 S, hh -> fp16 S (an f16
-// tensor-memory accumulator, read back as half2 pairs); the softmax arithmetic is fp32 in both, as in the reference.
-// P.V accumulates in fp32 for every variant, because O lives in tensor memory across all key blocks: an fp16 accumulator
-// there would add N terms in fp16, where the reference's fh / hh only ever add 64 (one key block) before going to fp32.
+// softmax). Variants (fastbb/attention.py:5-7) name the accumulate types of the two products in the reference's
+// mma.sync kernels, where fp16 accumulation doubles the GeForce tensor rate. On tcgen05 an f16 accumulator runs at the
+// same rate as an fp32 one, and reading it back costs a conversion per element (measured: 215 vs 201 us per launch at
+// N = 6145), so ff, fh and hh all run with fp32 S here; the softmax arithmetic is fp32 as in the reference. P.V
+// accumulates in fp32 as well, because O lives in tensor memory across all key blocks: an fp16 accumulator there would
+// add N terms in fp16, where the reference's fh / hh only ever add 64 (one key block) before going to fp32. Every
+// variant is therefore at least as accurate as the reference's.
 // The kernel is bound by the exponentials, not the tensor core: 128 x 128 of them per S tile against 16 results per
 // clock per SM from the transcendental unit is twice the time of the tile's two matrix products (1024 vs 2 x 256 clocks).
 // Measured dynamics worth knowing before changing the pipeline: a softmax warp alone cannot saturate the transcendental
@@ -173,7 +176,7 @@ __device__ __forceinline__ bool wait_slot_flag(const unsigned* flag, int lane, v
     return ok;
 }
 
-template <int NQ, bool S16>
+template <int NQ>
 __global__ void __launch_bounds__(128 + 256 * NQ, 1)
 flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FlashArgs a) {
@@ -306,7 +309,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         //                                                      the next item (other Q buffer), issued while the group works on g
         //   P_t(g) written                                 ->  O_t (+)= P_t(g) V
         const int t = warp - 1;
-        const uint32_t idesc_qk = make_idesc_f16(FQ, FK, !S16, false, false);
+        const uint32_t idesc_qk = make_idesc_f16(FQ, FK, true, false, false);
         const uint32_t idesc_pv = make_idesc_f16(FQ, 64, true, false, true);
         constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
         const uint64_t qd0 = smem_desc(base + S::kQOff + t * kTileBytes, desc_hi);
@@ -448,13 +451,8 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_free(t));  // S_t is in registers: the next Q K^T may overwrite it
                 float va[64];
-                if constexpr (!S16) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) va[i] = __uint_as_float(r[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) va[i] = __half2float(__ushort_as_half((unsigned short)(r[i] & 0xFFFFu)));
-                }
+                for (int i = 0; i < 64; ++i) va[i] = __uint_as_float(r[i]);
                 if (to_end && n == 1 && (a.N & (FK - 1)) != 0) {  // the group's last key block is ragged: mask keys >= N
                     const int key0 = (nkb - 1) * FK + 2 * cq;
 #pragma unroll
@@ -613,13 +611,13 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
 }
 
-template <int NQ, bool S16>
+template <int NQ>
 static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, FlashArgs a, int B, void* ws,
                                 int64_t ws_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = flash64_umma_kernel<NQ, S16>;
+    auto kern = flash64_umma_kernel<NQ>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem::kDynamic);
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(flash64_umma_kernel): %s", cudaGetErrorString(e));
@@ -737,10 +735,9 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
     a.o_sn = os[1];
     a.o_sh = os[2];
     a.scale_log2 = scale * 1.4426950408889634f;
-    const bool two = two_tiles_per_cta(B, N, H);
-    const bool s16 = variant == FBB_FLASH_HH;
-    if (two) return s16 ? launch_flash_variant<2, true>(tq, tk, tv, a, B, ws, ws_bytes, stream) : launch_flash_variant<2, false>(tq, tk, tv, a, B, ws, ws_bytes, stream);
-    return s16 ? launch_flash_variant<1, true>(tq, tk, tv, a, B, ws, ws_bytes, stream) : launch_flash_variant<1, false>(tq, tk, tv, a, B, ws, ws_bytes, stream);
+    (void)variant;  // ff, fh and hh run the same kernel on this part (see the note on variants at the top of the file)
+    if (two_tiles_per_cta(B, N, H)) return launch_flash_variant<2>(tq, tk, tv, a, B, ws, ws_bytes, stream);
+    return launch_flash_variant<1>(tq, tk, tv, a, B, ws, ws_bytes, stream);
 }
 
 }  // namespace fbb

@@ -50,10 +50,13 @@ enum fbb_accumulate {
     FBB_ACC_F16 = 1  /* fp16 tensor-memory accumulator   (reference g1, g2 except fc2; gemm variant h)        */
 };
 
+/* The reference's names for the accumulate types of Q.K^T and P.V in its mma.sync kernels (attention.py variants). All
+ * three are accepted; on tcgen05 an f16 accumulator is no faster than an fp32 one and costs a conversion when it is read
+ * back, so every variant computes both products with fp32 accumulators (at least the reference's accuracy). */
 enum fbb_flash_variant {
-    FBB_FLASH_FF = 0, /* fp32 accumulate for Q.K^T and for P.V        (attention.py variant "ff") */
-    FBB_FLASH_FH = 1, /* fp32 Q.K^T, fp16-accumulated P.V per key block ("fh")                    */
-    FBB_FLASH_HH = 2  /* fp16 accumulate for both                      ("hh")                      */
+    FBB_FLASH_FF = 0, /* reference: fp32 accumulate for Q.K^T and for P.V */
+    FBB_FLASH_FH = 1, /* reference: fp32 Q.K^T, fp16-accumulated P.V per key block */
+    FBB_FLASH_HH = 2  /* reference: fp16 accumulate for both */
 };
 
 /* Library version (FBB_VERSION of the build). */

@@ -241,7 +241,7 @@ def test_flash_matches_oracle(oracle, variant, B, N, H):
     o = attention(qd, kd, vd, scale=0.125, variant=variant, out=out)
     q, k, v = qkv.unbind(2)
     want = oracle.attention(q, k, v, scale=0.125)
-    assert oracle.rel_l2(o.cpu().float(), want) < (TOL_F16 if variant == "hh" else TOL_F32)
+    assert oracle.rel_l2(o.cpu().float(), want) < TOL_F32   # every variant accumulates in fp32 on this part
     assert not torch.isnan(o).any()
     check()
     status_ok()
@@ -267,7 +267,7 @@ def test_flash_peaked_rows_default_scale_and_bhnd_layout(oracle, variant):
     o = attention_bhnd(q.to(dev()), k.to(dev()), v.to(dev()), variant=variant)
     want = oracle.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
     assert o.shape == (1, 4, 300, 64)
-    assert oracle.rel_l2(o.cpu().float(), want) < (TOL_F16 if variant == "hh" else 2e-3)
+    assert oracle.rel_l2(o.cpu().float(), want) < 2e-3
 
 
 @pytest.mark.parametrize("variant", ["ff", "fh", "hh"])
@@ -283,11 +283,11 @@ def test_flash_full_size_properties(variant, N):
     v = torch.randn(1, N, H, 64, device=dev(), generator=g).half()
     ones = torch.full_like(v, 0.5)
     o = attention(q, k, ones, scale=0.125, variant=variant).float()
-    assert (o - 0.5).abs().max() < (4e-3 if variant != "ff" else 1.5e-3)
+    assert (o - 0.5).abs().max() < 1.5e-3
     perm = torch.randperm(N, device=dev(), generator=g)
     o1 = attention(q, k, v, scale=0.125, variant=variant).float()
     o2 = attention(q, k[:, perm], v[:, perm], scale=0.125, variant=variant).float()
-    assert (o1 - o2).norm() / o1.norm() < (TOL_F16 if variant == "hh" else 2e-3)
+    assert (o1 - o2).norm() / o1.norm() < 2e-3
     same_k = k[:, :1].expand(1, N, H, 64).contiguous()
     o3 = attention(q, same_k, v, scale=0.125, variant=variant).float()
     mean_v = v.float().mean(dim=1, keepdim=True)
@@ -324,7 +324,7 @@ def test_flash_split_form_matches_one_cta_per_group(oracle, variant, B, N, H):
     assert torch.equal(default, split)
     if B * H * N * N <= 2 * 11 * 2500 * 2500:
         q, k, v = qkv.unbind(2)
-        assert oracle.rel_l2(split.cpu().float(), oracle.attention(q, k, v, scale=0.125)) < (TOL_F16 if variant == "hh" else TOL_F32)
+        assert oracle.rel_l2(split.cpu().float(), oracle.attention(q, k, v, scale=0.125)) < TOL_F32
     with pytest.raises(_lib.FastbbError):                                # a workspace that is too small is rejected, not ignored
         _lib.check(_lib.load().fbb_flash64_f16_ws(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), B, N, H,
                                                   *qd.stride()[:3], *kd.stride()[:3], *vd.stride()[:3], *out.stride()[:3],
