@@ -306,7 +306,10 @@ class FastViT:
     def run(self, x, layers, norm=True):
         """-> list of tokens [B, 1 + nreg + HW, C] after the blocks in `layers` (normed with vit.norm if norm)."""
         out = []
-        last = max(layers)
+        layers = sorted(l for l in set(layers) if 0 <= l < len(self.blocks))  # as the reference's loop: others never match
+        if not layers:
+            return out
+        last = layers[-1]
         with torch.autocast("cuda", enabled=False):
             t = self.tokens(x).contiguous()
             # One C call per run of blocks between two selected layers (t is this function's own buffer, updated in
@@ -314,7 +317,7 @@ class FastViT:
             use_runner = os.environ.get("FBB_NO_RUNNER") != "1"
             i = 0
             while i <= last:
-                j = min([l for l in layers if l >= i])  # next selected layer
+                j = min(l for l in layers if l >= i)  # next selected layer
                 if not (use_runner and run_stack(self.blocks[i:j + 1], t, self.attn, self.gacc)):
                     use_runner = False
                     for b in self.blocks[i:j + 1]:
