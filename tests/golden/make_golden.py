@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself (its friendly fp32 CPU tier).
 
-    python tests/golden/make_golden.py [/path/to/reference]        (default /root/reference)
+    python tests/golden/make_golden.py /path/to/reference          (a checkout of fastforks/fastbb; or $FASTBB_REFERENCE)
 
 The reference is a Python package whose fp32 tier needs no GPU: FastViT(attn="sdpa", gacc=False, dtype=float32)
 (fastbb/vit.py:42,108-150), install_vit_blocks(model, "sdpa-g0", convert=False) (fastbb/vit.py:311-328), gemm.linear
@@ -136,4 +136,7 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FASTBB_REFERENCE")
+    if not ref:
+        sys.exit("usage: make_golden.py /path/to/reference  (a checkout of fastforks/fastbb)")
+    main(ref)
