@@ -402,7 +402,13 @@ class _BlockCfg:
         _gemm_variants(gacc)
         self.attn, self.gacc = attn, gacc
 
-    def block(self, b, x):
+    def block(self, b, x, own=False):
+        """One block on x [B, N, C] fp16 contiguous -> new tensor. `own`: x is a private copy the call may overwrite.
+        One C call (fbb_block_forward_f16's table form) when the block is of the form the runner covers, else seven."""
+        if x.dim() == 3 and os.environ.get("FBB_NO_RUNNER") != "1":
+            t = x if own else x.clone()
+            if run_stack([b], t, self.attn, self.gacc):
+                return t
         return run_block(b, x, self.attn, self.gacc)
 
 
@@ -450,7 +456,8 @@ def _fast_block_forward(self, x, *args, **kw):
     caller_dtype = x.dtype
     with torch.autocast("cuda", enabled=False):
         wd = self.attn.qkv.weight.dtype
-        y = cfg.block(self, x.to(wd).contiguous())
+        xc = x.to(wd).contiguous()
+        y = cfg.block(self, xc, own=xc.data_ptr() != x.data_ptr())  # a cast or compaction made a private copy already
     return y if caller_dtype == wd else y.to(caller_dtype)
 
 
