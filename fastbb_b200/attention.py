@@ -26,7 +26,7 @@ def _ok(t):
             and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0)
 
 
-_WORKSPACES = {}  # (device index, stream handle) -> zeroed uint8 tensor; the kernel leaves it zeroed after every launch
+_WORKSPACES = {}  # (device index, stream handle) -> uint8 tensor, zeroed when created; every launch leaves its flag words zero again
 
 
 def _workspace(device, need):
