@@ -14,6 +14,10 @@ and LayerNorm at the shapes the ViT configs produce, timed with CUDA events and 
 (c) LayerNorm: hidden 1024, M = 6145; bytes = M C (2 + 2).
 Between timed launches a 256 MB buffer is overwritten when --flush-l2 is given (default: inputs stay L2-resident, as
 they are inside the block stack where each kernel reads what the previous one just wrote).
+--torch adds, for every case, the PyTorch library path for the same operator on the same tensors in the same process
+(what the reference's friendly tier launches, fastbb/vit.py:114-143): F.linear followed by the separate F.gelu and
+addcmul passes the fused epilogues replace (`torch_gemm_us` is the F.linear call alone), F.scaled_dot_product_attention,
+F.layer_norm; the line then carries `torch_us` and `ratio` = torch_us / us.
 """
 import argparse
 import json
@@ -49,11 +53,14 @@ def main():
     ap.add_argument("--k", type=int)
     ap.add_argument("--nn", type=int)
     ap.add_argument("--act", default=None)
+    ap.add_argument("--res", action="store_true", help="linear: with the LayerScale + residual epilogue (res + gamma * y)")
     ap.add_argument("--acc", default=None)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--torch", action="store_true", help="also time the PyTorch library operators on the same tensors")
     args = ap.parse_args()
+    import torch.nn.functional as F
 
     dev = torch.device("cuda:0")
     tf_peak, gb_peak, src = peaks()
@@ -107,8 +114,13 @@ def main():
             for variant in ([args.variant] if args.variant else ["ff", "fh", "hh"]):
                 ms = timed(lambda: attention(q, k, v, scale=0.125, variant=variant, out=out))
                 tf = 4.0 * args.batch * N * N * args.heads * 64 / (ms * 1e-3) / 1e12
+                extra = {}
+                if args.torch:
+                    qt, kt, vt = (t.transpose(1, 2) for t in (q, k, v))   # [B, H, N, 64] views, as the reference's SDPA path passes them
+                    tms = timed(lambda: F.scaled_dot_product_attention(qt, kt, vt, scale=0.125))
+                    extra = dict(torch_us=tms * 1e3, ratio=tms / ms, torch_what="F.scaled_dot_product_attention")
                 emit(kernel="flash64", variant=variant, B=args.batch, N=N, H=args.heads, us=ms * 1e3, tflops=tf,
-                     frac_of_measured_burst=tf / tf_peak, frac_of_nominal_2250=tf / 2250.0)
+                     frac_of_measured_burst=tf / tf_peak, frac_of_nominal_2250=tf / 2250.0, **extra)
     if args.only in (None, "linear"):
         shapes = [(args.k, args.nn)] if args.k and args.nn else [(1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024)]
         for M in ([args.m] if args.m else [257, 1370, 6145, 32768]):
@@ -118,11 +130,27 @@ def main():
                 b = torch.zeros(N, device=dev, dtype=torch.float16)
                 n_out = N // 2 if args.act == "swiglu" else N
                 out = torch.empty(M, n_out, device=dev, dtype=torch.float16)
+                res = torch.randn(M, n_out, device=dev, generator=g).half() if args.res else None
+                gam = (0.05 + 0.15 * torch.rand(n_out, device=dev, generator=g)).half() if args.res else None
+                extra = {}
+                if args.torch:
+                    def torch_path():
+                        y = F.linear(x, w, b)
+                        if args.act == "gelu":
+                            y = F.gelu(y)
+                        elif args.act == "swiglu":
+                            x1, x2 = y.chunk(2, dim=-1)
+                            y = F.silu(x1).mul_(x2)
+                        return torch.addcmul(res, y, gam) if res is not None else y
+                    tms, gms = timed(torch_path), timed(lambda: F.linear(x, w, b))
+                    extra = dict(torch_us=tms * 1e3, torch_gemm_us=gms * 1e3, torch_what="F.linear + separate activation / addcmul passes")
                 for acc in ([args.acc] if args.acc else ["f32", "h"]):
-                    ms = timed(lambda: linear(x, w, b, act=args.act, variant=acc, out=out))
+                    ms = timed(lambda: linear(x, w, b, act=args.act, res=res, gamma=gam, variant=acc, out=out))
                     tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
-                    emit(kernel="linear", acc=acc, act=args.act, M=M, N=N, K=K, us=ms * 1e3, tflops=tf,
-                         frac_of_measured_burst=tf / tf_peak, frac_of_nominal_2250=tf / 2250.0)
+                    if extra:
+                        extra["ratio"] = extra["torch_us"] / (ms * 1e3)
+                    emit(kernel="linear", acc=acc, act=args.act, res=bool(args.res), M=M, N=N, K=K, us=ms * 1e3, tflops=tf,
+                         frac_of_measured_burst=tf / tf_peak, frac_of_nominal_2250=tf / 2250.0, **extra)
     if args.only in (None, "layernorm"):
         M, C = args.m or 6145, args.k or 1024
         x = torch.randn(M, C, device=dev, generator=g).half()
@@ -130,8 +158,12 @@ def main():
         out = torch.empty_like(x)
         ms = timed(lambda: layer_norm(x, w, b, 1e-6, out=out))
         gbs = M * C * 4.0 / (ms * 1e-3) / 1e9
+        extra = {}
+        if args.torch:
+            tms = timed(lambda: F.layer_norm(x, (C,), w, b, 1e-6))
+            extra = dict(torch_us=tms * 1e3, ratio=tms / ms, torch_what="F.layer_norm")
         emit(kernel="layernorm", M=M, C=C, us=ms * 1e3, gbs=gbs, frac_of_measured_copy=gbs / gb_peak, frac_of_nominal_8000=gbs / 8000.0,
-             bytes=M * C * 4)
+             bytes=M * C * 4, **extra)
 
 
 if __name__ == "__main__":

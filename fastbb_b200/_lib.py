@@ -52,8 +52,11 @@ PROTOTYPES = {
     "fbb_status_string": (ctypes.c_char_p, [_i32]),
     "fbb_last_error": (ctypes.c_char_p, []),
     "fbb_device_status": (_i32, [ctypes.POINTER(ctypes.c_uint * 4)]),
+    "fbb_diag_wait_timeout": (_i32, [ctypes.c_uint64, ctypes.c_uint, _vp]),
+    "fbb_diag_sm_clock_mhz": (_i32, [_vp, _i64, _vp]),
     "fbb_linear_max_cta_pairs": (_i32, [_i32]),
     "fbb_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _f32, _i32, _i32, _vp]),
+    "fbb_layernorm_split_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32, _vp]),
     "fbb_linear_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
@@ -83,7 +86,8 @@ def launched(n=1):
 
 
 # what libfastbb_flash64.so exports (the other prototypes are skipped when that library is the one loaded)
-FLASH_ONLY_SYMBOLS = ("fbb_version", "fbb_status_string", "fbb_last_error", "fbb_device_status", "fbb_flash64_f16",
+FLASH_ONLY_SYMBOLS = ("fbb_version", "fbb_status_string", "fbb_last_error", "fbb_device_status", "fbb_diag_wait_timeout",
+                      "fbb_diag_sm_clock_mhz", "fbb_flash64_f16",
                       "fbb_flash64_workspace_bytes", "fbb_flash64_f16_ws", "fbb_flash64_f16_static")
 
 

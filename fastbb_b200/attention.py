@@ -12,10 +12,19 @@ Small inputs run the same kernel with one 128-query tile per CTA instead of the 
 scale <= 0) raises instead of falling back to torch (fastbb/attention.py:38-48).
 
 When the query tiles do not fill the SMs evenly (ViT-L/14 at 896x1344: 400 CTAs of work on 148 SMs) the kernel runs in
-its split form, which needs ~11 MB of scratch memory: `attention` keeps one zero-initialised workspace per (device,
-stream) for that and hands it to fbb_flash64_f16_ws; `workspace=False` selects the plain one-CTA-per-tile form,
-`workspace=<uint8 CUDA tensor>` lends a caller-owned (zeroed) one.
+its split form, which needs ~11 MB of scratch memory, handed to fbb_flash64_f16_ws. Calls that may overlap on the GPU
+must not share that memory, so where it comes from depends on the caller:
+  * `workspace=<uint8 CUDA tensor>` lends a caller-owned (zeroed) one; `workspace=False` selects the plain
+    one-CTA-per-tile form, which needs none;
+  * inside `with use_workspaces(owner):` (what FastViT.run and graphs.Graphed do) it comes from `owner`, a
+    `Workspaces` object: one buffer per device, created and zeroed OUTSIDE any stream capture (the warm-up call before a
+    capture creates it), so that a captured graph bakes in memory its owner keeps alive and no other graph uses;
+  * otherwise (plain eager calls) from a small per-(device, stream) table of this module, oldest entry evicted first.
 """
+import collections
+import contextlib
+import threading
+
 import torch
 
 from . import _lib
@@ -26,14 +35,54 @@ def _ok(t):
             and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0)
 
 
-_WORKSPACES = {}  # (device index, stream handle) -> uint8 tensor, zeroed when created; every launch leaves its flag words zero again
+class Workspaces:
+    """Split-form scratch memory owned by one caller (a FastViT, a Graphed): one zeroed uint8 buffer per device. An owner's
+    calls are expected to be ordered on one stream at a time (a model instance is not re-entrant); two owners never share."""
+
+    def __init__(self):
+        self._by_device = {}
+
+    def get(self, device, need):
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        ws = self._by_device.get(idx)
+        if ws is None or ws.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the attention workspace must exist before a stream capture starts: run the same call once "
+                                   "outside the capture first (FastViT.run_graphed and graphs.Graphed do)")
+            ws = self._by_device[idx] = torch.zeros(need, device=device, dtype=torch.uint8)
+        return ws
+
+
+_ACTIVE = threading.local()                 # .owner: the Workspaces of the innermost use_workspaces() block of this thread
+_EAGER = collections.OrderedDict()          # (device index, stream handle) -> uint8 tensor, for calls outside any owner
+_EAGER_MAX = 8
+
+
+@contextlib.contextmanager
+def use_workspaces(owner):
+    """Attention calls made inside the block (by this thread) take their scratch memory from `owner` (a Workspaces)."""
+    prev = getattr(_ACTIVE, "owner", None)
+    _ACTIVE.owner = owner
+    try:
+        yield owner
+    finally:
+        _ACTIVE.owner = prev
 
 
 def _workspace(device, need):
+    owner = getattr(_ACTIVE, "owner", None)
+    if owner is not None:
+        return owner.get(device, need)
     key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(device).cuda_stream)
-    ws = _WORKSPACES.get(key)
+    ws = _EAGER.get(key)
     if ws is None or ws.numel() < need:
-        ws = _WORKSPACES[key] = torch.zeros(need, device=device, dtype=torch.uint8)
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("attention() inside a stream capture needs a workspace that outlives the graph: wrap the call in "
+                               "use_workspaces(...) with one made before the capture, or pass workspace=")
+        ws = _EAGER[key] = torch.zeros(need, device=device, dtype=torch.uint8)
+        while len(_EAGER) > _EAGER_MAX:
+            _EAGER.popitem(last=False)
+    _EAGER.move_to_end(key)
     return ws
 
 

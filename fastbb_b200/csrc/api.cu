@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "internal.h"
@@ -30,10 +31,58 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Encoded tensor maps are kept in a small direct-mapped table: a map is a pure function of (base, rank, dims, strides,
+// box, swizzle), so a hit can never be stale, and a block stack asks for the same few dozen maps on every call (the
+// driver call costs microseconds, which is what an eager small-model forward is made of). The table is the one piece of
+// mutable state shared between calls; a mutex guards it.
+namespace {
+struct TmapKey {
+    const void* base;
+    uint64_t dims[4];
+    int64_t strides[4];
+    uint32_t box[4];
+    int rank, swizzle;
+    bool operator==(const TmapKey& o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapEntry {
+    TmapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int kTmapSlots = 2048;
+TmapEntry g_tmap_cache[kTmapSlots];
+std::mutex g_tmap_mutex;
+uint64_t tmap_hash(const TmapKey& k) {
+    uint64_t h = 1469598103934665603ull;
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(&k);
+    for (size_t i = 0; i < sizeof(TmapKey); ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
+}
+}  // namespace
+
 int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
                   const uint32_t* box, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+    if (rank < 1 || rank > 4) return fail(FBB_ERR_SHAPE, "tensor map rank %d not supported", rank);
+    TmapKey key;
+    memset(&key, 0, sizeof(key));  // padding bytes too: the key is compared and hashed as raw bytes
+    key.base = base;
+    key.rank = rank;
+    key.swizzle = (int)swizzle;
+    for (int i = 0; i < rank; ++i) {
+        key.dims[i] = dims[i];
+        key.strides[i] = i > 0 ? strides_elems[i] : 1;
+        key.box[i] = box[i];
+    }
+    TmapEntry& slot = g_tmap_cache[tmap_hash(key) % kTmapSlots];
+    {
+        std::lock_guard<std::mutex> lock(g_tmap_mutex);
+        if (slot.used && slot.key == key) {
+            *map = slot.map;
+            return FBB_OK;
+        }
+    }
     cuuint64_t gdim[5];
     cuuint64_t gstr[4];
     cuuint32_t bx[5];
@@ -48,6 +97,10 @@ int make_tmap_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* 
                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(FBB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
     return FBB_OK;
 }
 
@@ -73,6 +126,36 @@ bool pdl_enabled() {
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Diagnostics. wait_timeout_probe_kernel: one warp initialises an mbarrier that nothing ever arrives on and waits for it
+// with the library's bounded wait and a caller-given limit; the wait gives up, records DEV_TIMEOUT_OTHER with `detail`
+// in the status word and the kernel returns normally. This is the path every pipeline wait takes when it runs out.
+__global__ void wait_timeout_probe_kernel(unsigned long long limit_ns, unsigned int detail, unsigned int* gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        const bool done = mbar_wait_limit(smem_u32(&bar), 0u, &abort_flag, DEV_TIMEOUT_OTHER, detail, limit_ns);
+        if (gave_up != nullptr) *gave_up = done ? 0u : 1u;
+    }
+}
+
+// sm_clock_probe_kernel: one thread counts `spin_clocks` SM clocks against the nanosecond timer and stores the ratio in
+// MHz: the SM clock the kernels around it on the stream actually ran at (the driver's sampled clock reading is too
+// coarse to tell a power-capped stretch of a few milliseconds from an uncapped one).
+__global__ void sm_clock_probe_kernel(float* out_mhz, long long spin_clocks) {
+    const uint64_t t0 = globaltimer_ns();
+    const long long c0 = clock64();
+    long long c1 = c0;
+    while (c1 - c0 < spin_clocks) c1 = clock64();  // ends after spin_clocks clocks: the counter always advances
+    const uint64_t t1 = globaltimer_ns();
+    *out_mhz = t1 > t0 ? (float)((double)(c1 - c0) * 1000.0 / (double)(t1 - t0)) : 0.f;
+}
 
 }  // namespace fbb
 
@@ -132,6 +215,17 @@ int fbb_layernorm_f16(const void* x, void* y, const void* w, const void* b, int6
     return launch_layernorm(x, y, w, b, M, C, ldx, ldy, eps, in_dtype, param_dtype, (cudaStream_t)stream);
 }
 
+int fbb_layernorm_split_f16(const void* x, const void* w, const void* b, void* patches_out, void* cls_out, void* regs_out, int B, int N,
+                            int C, int n_prefix, float eps, int apply_norm, int channel_major, void* stream) {
+    if (x == nullptr || patches_out == nullptr) return fail(FBB_ERR_NULL, "layernorm_split: x or patches_out is null");
+    if (B < 0 || N < 0 || C <= 0 || (C & 7) != 0 || C > 2048) return fail(FBB_ERR_SHAPE, "layernorm_split: need B, N >= 0 and C %% 8 == 0, C <= 2048 (B=%d N=%d C=%d)", B, N, C);
+    if (n_prefix < 1 || n_prefix > 32 || (N > 0 && n_prefix > N)) return fail(FBB_ERR_SHAPE, "layernorm_split: n_prefix (cls + registers) must be in [1, min(32, N)], got %d", n_prefix);
+    if (!aligned16(x) || !aligned16(w) || !aligned16(b) || !aligned16(cls_out) || !aligned16(regs_out)) return fail(FBB_ERR_ALIGN, "layernorm_split: pointers must be 16-byte aligned");
+    if (channel_major ? (reinterpret_cast<uintptr_t>(patches_out) & 1u) != 0 : !aligned16(patches_out)) return fail(FBB_ERR_ALIGN, "layernorm_split: patches_out is misaligned");
+    if (!(eps >= 0.f)) return fail(FBB_ERR_SHAPE, "layernorm_split: eps must be >= 0");
+    return launch_layernorm_split(x, w, b, patches_out, cls_out, regs_out, B, N, C, n_prefix, eps, apply_norm != 0, channel_major != 0, (cudaStream_t)stream);
+}
+
 int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
                    int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
                    void* stream) {
@@ -156,20 +250,28 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
 
 int64_t fbb_flash64_workspace_bytes(int B, int N, int H) { return flash64_workspace_bytes_for(B, N, H); }
 
-int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
-                       int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
-                       int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace, int64_t workspace_bytes,
-                       void* stream) {
+// Host-side checks shared by the three attention entry points; FBB_OK means the launch may go ahead.
+static int check_flash_args(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs, const int64_t* ks,
+                            const int64_t* vs, const int64_t* os, float scale, int variant) {
     if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return fail(FBB_ERR_NULL, "flash64: q, k, v or o is null");
     if (variant < FBB_FLASH_FF || variant > FBB_FLASH_HH) return fail(FBB_ERR_ENUM, "flash64: unknown variant %d", variant);
     if (B < 0 || N < 0 || H <= 0 || (int64_t)B * H > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: bad B/N/H (%d, %d, %d)", B, N, H);
     if (!(scale > 0.f)) return fail(FBB_ERR_SHAPE, "flash64: scale must be > 0");
-    const int64_t qs[3] = {q_sb, q_sn, q_sh}, ks[3] = {k_sb, k_sn, k_sh}, vs[3] = {v_sb, v_sn, v_sh}, os[3] = {o_sb, o_sn, o_sh};
     for (int i = 0; i < 3; ++i)
         if ((qs[i] & 7) || (ks[i] & 7) || (vs[i] & 7) || (os[i] & 7) || qs[i] < 0 || ks[i] < 0 || vs[i] < 0 || os[i] < 0)
             return fail(FBB_ERR_ALIGN, "flash64: strides must be non-negative multiples of 8 elements");
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(FBB_ERR_ALIGN, "flash64: pointers must be 16-byte aligned");
-    if (q_sn < 64 || k_sn < 64 || v_sn < 64 || o_sn < 64) return fail(FBB_ERR_SHAPE, "flash64: token stride smaller than the head dimension");
+    if (qs[1] < 64 || ks[1] < 64 || vs[1] < 64 || os[1] < 64) return fail(FBB_ERR_SHAPE, "flash64: token stride smaller than the head dimension");
+    return FBB_OK;
+}
+
+int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
+                       int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
+                       int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace, int64_t workspace_bytes,
+                       void* stream) {
+    const int64_t qs[3] = {q_sb, q_sn, q_sh}, ks[3] = {k_sb, k_sn, k_sh}, vs[3] = {v_sb, v_sn, v_sh}, os[3] = {o_sb, o_sn, o_sh};
+    const int rc = check_flash_args(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant);
+    if (rc != FBB_OK) return rc;
     if (workspace != nullptr && (!aligned16(workspace) || workspace_bytes < 0)) return fail(FBB_ERR_ALIGN, "flash64: workspace must be 16-byte aligned");
     if (B == 0 || N == 0) return FBB_OK;
     return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, workspace, workspace_bytes, (cudaStream_t)stream);
@@ -185,15 +287,31 @@ int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B,
 int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
                            int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
                            int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* stream) {
-    if (B < 0 || N < 0 || H <= 0) return fail(FBB_ERR_SHAPE, "flash64: bad B/N/H (%d, %d, %d)", B, N, H);
+    // every argument is checked before the array is looked up or anything is enqueued: a rejected call leaves no trace
+    const int64_t qs[3] = {q_sb, q_sn, q_sh}, ks[3] = {k_sb, k_sn, k_sh}, vs[3] = {v_sb, v_sn, v_sh}, os[3] = {o_sb, o_sn, o_sh};
+    const int rc0 = check_flash_args(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant);
+    if (rc0 != FBB_OK) return rc0;
+    if (B == 0 || N == 0) return FBB_OK;
     void* ws = nullptr;
     int64_t ws_bytes = 0;
-    if (flash64_workspace_bytes_for(B, N, H) > 0) {  // only shapes that are split touch the workspace
+    if (flash64_workspace_bytes_for(B, N, H) > 0) {  // only shapes that are split touch the array
         const int rc = flash64_static_workspace(&ws, &ws_bytes, (cudaStream_t)stream);
         if (rc != FBB_OK) return rc;
     }
-    return fbb_flash64_f16_ws(q, k, v, o, B, N, H, q_sb, q_sn, q_sh, k_sb, k_sn, k_sh, v_sb, v_sn, v_sh, o_sb, o_sn, o_sh, scale, variant, ws,
-                              ws_bytes, stream);
+    return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+int fbb_diag_wait_timeout(uint64_t limit_ns, unsigned int detail, void* stream) {
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail(FBB_ERR_SHAPE, "diag: limit must be in (0, 100 ms]");
+    wait_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, detail, nullptr);
+    return cuda_status(cudaGetLastError());
+}
+
+int fbb_diag_sm_clock_mhz(float* out_mhz, int64_t spin_clocks, void* stream) {
+    if (out_mhz == nullptr) return fail(FBB_ERR_NULL, "diag: out_mhz is null");
+    if (spin_clocks < 1024 || spin_clocks > (1ll << 24)) return fail(FBB_ERR_SHAPE, "diag: spin_clocks must be in [1024, 2^24]");
+    sm_clock_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(out_mhz, (long long)spin_clocks);
+    return cuda_status(cudaGetLastError());
 }
 
 #ifndef FBB_FLASH_ONLY

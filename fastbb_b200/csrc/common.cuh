@@ -52,6 +52,12 @@ __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.
 // allocation, descriptor prefetch) overlaps that tail, everything after it sees the previous kernel's memory.
 // Without the attribute the instruction does nothing.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the NEXT kernel of the stream (launched with the same attribute) be scheduled as soon as every CTA of this grid
+// has executed this or exited, instead of at the end of the grid: its CTAs then start on each SM as this grid's CTAs
+// leave it, and their set-up runs under this grid's tail. The next kernel still sees this grid's memory only after its
+// own griddepcontrol.wait, which returns when this grid has completed. Every kernel here issues it right after its own
+// wait: nothing a kernel does before its wait touches global memory.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -84,9 +90,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Wait limit: 2 s of wall time (checked every 256 polls). A healthy pipeline never comes near it.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// Returns true when the phase with `parity` completed; false after the limit (error recorded, *abort set).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code,
-                                          unsigned int detail) {
+// Returns true when the phase with `parity` completed; false after `limit_ns` (error recorded, *abort set).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code,
+                                                unsigned int detail, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
     for (;;) {
@@ -94,13 +100,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             report_error(code, detail);
             *abort_flag = 1;
             __threadfence_block();
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code,
+                                          unsigned int detail) {
+    return mbar_wait_limit(bar, parity, abort_flag, code, detail, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------------------------------------- proxies / fences

@@ -46,7 +46,13 @@
 // unit, so the two tiles run fastest half a period apart (2800 clocks per unit); in step, every phase collides with its
 // twin (3800 clocks). The half-period offset set at start-up is not stable: over some tens of units the later tile
 // catches up. CTAs that live for one group (<= ~130 units) mostly keep it; the persistent form loses part of what it
-// gains from the removed wave this way. Forcing strict turns with an extra barrier pair costs more than it saves (3100).
+// gains from the removed wave this way. Every way of forcing the offset that was built measured slower than letting the
+// tiles run free (N = 6145, 16 heads, 198-200 us free): strict turns around a whole unit (3100 clocks per unit); turns
+// around the exponential loop only, per SM sub-partition, so that one tile's load / maximum / store phases fall under the
+// other's exponentials (218 us: the two warps a tile has on a sub-partition do not saturate its transcendental unit on
+// their own, four contending warps use it better); a one-sided lock that only holds a tile back until the other is
+// 4/16 .. 14/16 of the way through its exponentials (201-212 us). Batching the exponentials in the source (arguments,
+// then exponentials, then sums) compiles to the same schedule; writing P back in two halves costs a second wait (212 us).
 #include "common.cuh"
 #include <cstdlib>
 
@@ -68,8 +74,13 @@ constexpr float kLazyMax = 8.0f;          // raise the running maximum only beyo
 constexpr unsigned kEmuMask = FBB_EMU_MASK;  // e.g. 0x88: pairs 3 and 7 of 8 (25 %); 0: all on the transcendental unit
 // Register split of the 640-thread (NQ = 2) kernel. It is launched with 96 registers per thread (the most 20 warps can
 // get); setmaxnreg.inc WAITS until the CTA's own pool has the registers, so the split must fit in that pool or the
-// kernel never starts its softmax: 128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96.
-constexpr int kRegsCtl = 40, kRegsSoftmax = 104;
+// kernel never starts its softmax: 128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96. 32 / 112 measured 2 % faster than
+// 40 / 104 (197 vs 201 us at N = 6145): a softmax thread holds 64 scores and up to 32 packed probabilities.
+#ifndef FBB_REGS_CTL
+#define FBB_REGS_CTL 32
+#define FBB_REGS_SOFTMAX 112
+#endif
+constexpr int kRegsCtl = FBB_REGS_CTL, kRegsSoftmax = FBB_REGS_SOFTMAX;
 static_assert(128 * kRegsCtl + 512 * kRegsSoftmax <= 640 * 96, "setmaxnreg split exceeds the CTA's register pool");
 
 // tensor-memory columns of tile t: S_t (128 columns) at t * kColTileS, O_t (fp32, 64 columns) at kColO + t * kColTileOP,
@@ -250,6 +261,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
+    grid_launch_dependents();
 
     // Item list of this CTA (see TailItems): items [0, rounds) are whole groups, the rest come from the table.
     const int n_items = a.rounds + s_tail->n;

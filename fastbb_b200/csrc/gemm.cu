@@ -114,6 +114,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     grid_dependency_wait();  // the set-up above may overlap the previous kernel's tail; its outputs are visible from here
+    grid_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -217,14 +218,30 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (!SWIGLU) s_gamma[i] = (g.gamma != nullptr && in) ? __half2float(g.gamma[wrow]) : 1.f;
             }
             named_bar_sync(1, kEpiThreads);
-            if (!mbar_wait(tfull_bar(acc), acc_ph, s_abort, DEV_TIMEOUT_TMEM_FULL, acc)) break;
-            tc_fence_after();
             const int row = m0 + quad * 32 + lane;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             const bool row_ok = row < g.M;
             const __half* r_row = g.res != nullptr ? g.res + (int64_t)row * g.ldr : nullptr;
-#pragma unroll 1
-            for (int c0 = chalf * (kOutCols / 2); c0 < (chalf + 1) * (kOutCols / 2); c0 += 32) {
+            // The residual of this thread's row for all of its columns goes into registers BEFORE the wait for the accumulator:
+            // the loads (one 64-byte piece per thread and chunk, L2 latency each) then run under the tile's main loop instead
+            // of sitting, chunk after chunk, in the epilogue's critical path (measured: 4.7 us of an 18 us proj launch).
+            constexpr int kChunks = kOutCols / 2 / 32;
+            uint4 rr[SWIGLU ? 1 : kChunks][4];
+            if constexpr (!SWIGLU) {
+#pragma unroll
+                for (int ci = 0; ci < kChunks; ++ci) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int col = n0 + chalf * (kOutCols / 2) + ci * 32 + q * 8;
+                        rr[ci][q] = (r_row != nullptr && row_ok && col < g.n_out) ? *reinterpret_cast<const uint4*>(r_row + col) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            if (!mbar_wait(tfull_bar(acc), acc_ph, s_abort, DEV_TIMEOUT_TMEM_FULL, acc)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll
+            for (int ci = 0; ci < kChunks; ++ci) {
+                const int c0 = chalf * (kOutCols / 2) + ci * 32;
                 uint32_t r[32];
                 float v[32];
                 tmem_ld32(t_row + (uint32_t)c0, r);
@@ -254,14 +271,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
                     }
                 }
-                // residual + LayerScale on the columns that exist (n_out % 8 == 0: a group of 8 is all in or all out)
-                if (!SWIGLU && r_row != nullptr && row_ok) {
+                // residual + LayerScale (columns beyond n_out and rows beyond M hold zeros and are clipped by the store)
+                if constexpr (!SWIGLU) {
+                    if (r_row != nullptr) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int col = n0 + c0 + q * 8;
-                        if (col < g.n_out) {
-                            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + col);
-                            const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+                        for (int q = 0; q < 4; ++q) {
+                            const __half2* rh = reinterpret_cast<const __half2*>(&rr[ci][q]);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const float2 rf = __half22float2(rh[j]);
@@ -311,6 +326,284 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         tc_fence_after();
         if constexpr (CTA2) tmem_dealloc_pair<2 * BN>(tmem_base);
         else tmem_dealloc<2 * BN>(tmem_base);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Wide pair form: one CTA pair per work item, an item = 256 rows x `w` output columns (w a multiple of 32, up to 512),
+// held in two tensor-memory accumulators of wa and wb columns (wa + wb = w, each a multiple of 32 and at most 256) that
+// share the A operand. Not persistent: the grid is one cluster per item. It exists for shapes whose tile count is small
+// against the SM count, where fixed 256-column tiles quantise badly: M = 6145, N = 1024 is 25 x 4 pair tiles on 74 pairs
+// (two waves, the second a third full); as 24 x 3 items of 352 columns it is one wave, and per k-block a CTA stages
+// 16 KB of A and w x 64 bytes of W for w / 256 x 512 tensor clocks (55 bytes per clock at w = 352, against 96 for the
+// one-CTA 256-column tile and 64 for the pair tile).
+// The few rows beyond the last full 256-row tile (every ViT token count is a multiple of the tile height plus the cls
+// token) do not get a tile of their own, which would cost a whole item's time for one row: the epilogue warps, idle
+// during the main loop, compute them as dot products on the CUDA cores (`gemv_rows`, at most kGemvMaxRows).
+constexpr int kGemvMaxRows = 8;
+constexpr int kWideMaxCols = 512;
+
+struct WideArgs {
+    const __half* A;
+    const __half* W;
+    __half* C;
+    const __half* bias;
+    const __half* res;
+    const __half* gamma;
+    int M, N, K;
+    int64_t lda, ldw, ldc, ldr;
+    int act, acc_f16;
+    int w, wa, wb;             // item width and its two accumulators
+    int chunks;                // items per 256-row tile: ceil(N / w)
+    int gemv_row0, gemv_rows;  // rows [gemv_row0, gemv_row0 + gemv_rows) are left to the epilogue warps
+    int stages, stage_bytes;   // operand ring: stage = A tile (16 KB) | this CTA's wa/2 rows of W | its wb/2 rows of W
+};
+
+struct WideSmem {
+    static constexpr int kParamBytes = 2 * kWideMaxCols * 4;  // bias + gamma of the item's columns (fp32)
+    static constexpr int kStoreBytes = 8 * 32 * 32 * 2;       // one [32 x 32] fp16 staging tile per epilogue warp
+    static constexpr int kMaxStages = 8;
+    static constexpr int kNumBars = 2 * kMaxStages + 1;
+    static constexpr int kTailBytes = kParamBytes + kStoreBytes + kNumBars * 8 + 16;
+    static constexpr int kMaxDynamic = 227 * 1024;
+    static int stages_for(int stage_bytes) {
+        const int n = (kMaxDynamic - 1024 - kTailBytes) / stage_bytes;
+        return n > kMaxStages ? kMaxStages : n;
+    }
+    static int dynamic_bytes(int stages, int stage_bytes) { return 1024 + stages * stage_bytes + kTailBytes; }
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_wa,
+                        const __grid_constant__ CUtensorMap tmap_wb, const __grid_constant__ CUtensorMap tmap_c, const WideArgs g) {
+    using S = WideSmem;
+    const uint32_t rank = cluster_ctarank();
+    const int item = (int)(blockIdx.x >> 1);
+    const int mt = item / g.chunks;
+    const int n0 = (item - mt * g.chunks) * g.w;
+    const int m0 = mt * 2 * BM + (int)rank * BM;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - raw);
+    const int ring = g.stages * g.stage_bytes;
+    float* s_bias = reinterpret_cast<float*>(gen + ring);
+    float* s_gamma = s_bias + kWideMaxCols;
+    const int store_off = ring + S::kParamBytes;
+    const uint32_t bar0 = base + store_off + S::kStoreBytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (S::kMaxStages + s); };
+    const uint32_t tfull_bar = bar0 + 8u * (2 * S::kMaxStages);
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + store_off + S::kStoreBytes + S::kNumBars * 8);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(gen + store_off + S::kStoreBytes + S::kNumBars * 8 + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_kb = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < g.stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *s_abort = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_wa);
+        tma_prefetch_desc(&tmap_wb);
+        tma_prefetch_desc(&tmap_c);
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_alloc_pair<512>(smem_u32(const_cast<uint32_t*>(s_tmem)));
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    grid_dependency_wait();
+    grid_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one lane in each CTA)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            const int wrow_a = n0 + (int)rank * (g.wa / 2);
+            const int wrow_b = n0 + g.wa + (int)rank * (g.wb / 2);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
+                const uint32_t sa = base + s * g.stage_bytes;
+                if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * g.stage_bytes);  // the leader's barrier counts both CTAs' bytes
+                tma_load_2d_pair(sa, &tmap_a, full_bar(s), kb * BK, m0);
+                tma_load_2d_pair(sa + BM * BK * 2, &tmap_wa, full_bar(s), kb * BK, wrow_a);
+                if (g.wb > 0) tma_load_2d_pair(sa + BM * BK * 2 + g.wa * BK, &tmap_wb, full_bar(s), kb * BK, wrow_b);
+                if (++s == g.stages) { s = 0; ph ^= 1u; }
+            }
+            if (!ok) __nanosleep(20000);  // let copies already in flight land before the CTA leaves
+        }
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------------------------ UMMA issuer (leader CTA, warp-uniform)
+        const uint32_t idesc_a = make_idesc_f16(2 * BM, g.wa, !g.acc_f16, false, false);
+        const uint32_t idesc_b = make_idesc_f16(2 * BM, g.wb > 0 ? g.wb : 32, !g.acc_f16, false, false);
+        constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
+        const uint64_t adesc0 = smem_desc(base, desc_hi);
+        const uint32_t d_a = tmem_base, d_b = tmem_base + 256u;
+        auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+            if (!all_ok(mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_TMA_FULL, s))) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t adesc = adesc0 + (uint64_t)((s * g.stage_bytes) >> 4);
+            const uint64_t bdesc_a = adesc + (uint64_t)((BM * BK * 2) >> 4);
+            const uint64_t bdesc_b = bdesc_a + (uint64_t)((g.wa * BK) >> 4);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+                const uint32_t accumulate = (kb != 0 || k != 0) ? 1u : 0u;
+                umma_ss_pair_warp(d_a, adesc + 2u * k, bdesc_a + 2u * k, idesc_a, accumulate);
+                if (g.wb > 0) umma_ss_pair_warp(d_b, adesc + 2u * k, bdesc_b + 2u * k, idesc_b, accumulate);
+            }
+            umma_commit_pair_warp(empty_bar(s));  // frees the stage in both CTAs
+            if (++s == g.stages) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit_pair_warp(tfull_bar);  // both CTAs' accumulators complete
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ epilogue warps
+        const int ew = warp - 2;
+        const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const int et = threadIdx.x - 64;
+        // (1) while the main loop runs: the rows that have no tile, one output element per warp at a time
+        if (g.gemv_rows > 0) {
+            const int total_warps = (int)gridDim.x * 8;
+            const int nvec = g.K >> 3;
+            for (int o = (int)blockIdx.x * 8 + ew; o < g.gemv_rows * g.N; o += total_warps) {
+                const int mi = o / g.N, n = o - mi * g.N;
+                const int64_t m = g.gemv_row0 + mi;
+                const uint4* ap = reinterpret_cast<const uint4*>(g.A + m * g.lda);
+                const uint4* wp = reinterpret_cast<const uint4*>(g.W + (int64_t)n * g.ldw);
+                float acc = 0.f;
+                for (int v = lane; v < nvec; v += 32) {
+                    const uint4 av = ap[v];
+                    const uint4 wv = __ldg(wp + v);
+                    const __half2* ah = reinterpret_cast<const __half2*>(&av);
+                    const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 af = __half22float2(ah[j]), wf = __half22float2(wh[j]);
+                        acc = fmaf(af.x, wf.x, acc);
+                        acc = fmaf(af.y, wf.y, acc);
+                    }
+                }
+#pragma unroll
+                for (int sft = 16; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+                if (lane == 0) {
+                    float v = acc + (g.bias != nullptr ? __half2float(g.bias[n]) : 0.f);
+                    if (g.act == 1) v = gelu_erf(v);
+                    if (g.res != nullptr) v = fmaf(g.gamma != nullptr ? __half2float(g.gamma[n]) : 1.f, v, __half2float(g.res[m * g.ldr + n]));
+                    g.C[m * g.ldc + n] = __float2half_rn(v);
+                }
+            }
+        }
+        // (2) bias and gamma of the item's columns
+        for (int i = et; i < g.w; i += kEpiThreads) {
+            const int col = n0 + i;
+            const bool in = col < g.N;
+            s_bias[i] = (g.bias != nullptr && in) ? __half2float(g.bias[col]) : 0.f;
+            s_gamma[i] = (g.gamma != nullptr && in) ? __half2float(g.gamma[col]) : 1.f;
+        }
+        named_bar_sync(1, kEpiThreads);
+        // (3) the accumulators: 32-column chunks, even chunks to warps 0-3, odd chunks to warps 4-7
+        uint8_t* stage_gen = gen + store_off + ew * 2048;
+        const uint32_t stage_addr = base + store_off + ew * 2048;
+        // The residual of this thread's row goes into registers ahead of its use: the first kResRing chunks before the wait for
+        // the accumulators (their L2 latency then runs under the main loop), chunk i + kResRing as soon as chunk i is done.
+        const int row = m0 + quad * 32 + lane;
+        const bool row_ok = row < g.M;
+        const __half* r_row = (g.res != nullptr && row_ok) ? g.res + (int64_t)row * g.ldr : nullptr;
+        constexpr int kResRing = 4, kMaxChunks = kWideMaxCols / 64;
+        uint4 rr[kResRing][4];
+        auto load_res = [&](int ci, uint4* dst) {
+            const int c0 = (ew >> 2) * 32 + ci * 64;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int col = n0 + c0 + q * 8;
+                dst[q] = (r_row != nullptr && c0 < g.w && col < g.N) ? *reinterpret_cast<const uint4*>(r_row + col) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+#pragma unroll
+        for (int ci = 0; ci < kResRing; ++ci) load_res(ci, rr[ci]);
+        if (mbar_wait(tfull_bar, 0u, s_abort, DEV_TIMEOUT_TMEM_FULL, 0)) {
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll
+            for (int ci = 0; ci < kMaxChunks; ++ci) {
+                const int c0 = (ew >> 2) * 32 + ci * 64;
+                if (c0 >= g.w || n0 + c0 >= g.N) break;
+                uint32_t r[32];
+                float v[32];
+                tmem_ld32(t_row + (uint32_t)(c0 < g.wa ? c0 : 256 + c0 - g.wa), r);
+                tmem_wait_ld();
+                if (g.acc_f16) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __half2float(__ushort_as_half((unsigned short)(r[j] & 0xFFFFu)));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += s_bias[c0 + j];
+                if (g.act == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                }
+                if (g.res != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __half2* rh = reinterpret_cast<const __half2*>(&rr[ci % kResRing][q]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 rf = __half22float2(rh[j]);
+                            v[q * 8 + 2 * j] = fmaf(s_gamma[c0 + q * 8 + 2 * j], v[q * 8 + 2 * j], rf.x);
+                            v[q * 8 + 2 * j + 1] = fmaf(s_gamma[c0 + q * 8 + 2 * j + 1], v[q * 8 + 2 * j + 1], rf.y);
+                        }
+                    }
+                    if (ci + kResRing < kMaxChunks) load_res(ci + kResRing, rr[ci % kResRing]);
+                }
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
+                    o.y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
+                    o.z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
+                    o.w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
+                    *reinterpret_cast<uint4*>(stage_gen + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && m0 + quad * 32 < g.M) {
+                    tma_store_2d(&tmap_c, stage_addr, n0 + c0, m0 + quad * 32);
+                    bulk_commit();
+                }
+            }
+        }
+        if (lane == 0) bulk_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer may still be signalling this CTA's barriers / reading its operands
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair<512>(tmem_base);
     }
 }
 
@@ -370,6 +663,96 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     return FBB_OK;
 }
 
+// Pairs of the wide kernel that can be resident at once on the current device (0: cannot be launched).
+static int wide_max_pairs() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaFuncSetAttribute(linear_wide_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kMaxDynamic) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * num_sms());
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = WideSmem::kMaxDynamic;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, linear_wide_pair_kernel, &cfg) != cudaSuccess) n = 0;
+            cudaGetLastError();
+        }
+        cached[dev] = n > 0 ? n : -1;
+    }
+    return cached[dev] > 0 ? cached[dev] : 0;
+}
+
+// Rows the wide form leaves to its epilogue warps: the remainder beyond the last full 256-row tile when it is small.
+static int wide_gemv_rows(int64_t M) {
+    const int r = (int)(M % (2 * BM));
+    return (M >= 2 * BM && r > 0 && r <= kGemvMaxRows) ? r : 0;
+}
+static int64_t wide_row_tiles(int64_t M) { return wide_gemv_rows(M) > 0 ? M / (2 * BM) : (M + 2 * BM - 1) / (2 * BM); }
+
+static int launch_wide(const void* A, const void* W, void* C, const GemmArgs& base, int64_t lda, int64_t ldw, int w, cudaStream_t stream) {
+    if (wide_max_pairs() == 0) return fail(FBB_ERR_SHAPE, "linear: this device cannot co-schedule CTA pairs");
+    WideArgs g;
+    g.A = reinterpret_cast<const __half*>(A);
+    g.W = reinterpret_cast<const __half*>(W);
+    g.C = base.C;
+    g.bias = base.bias;
+    g.res = base.res;
+    g.gamma = base.gamma;
+    g.M = base.M;
+    g.N = base.N;
+    g.K = base.K;
+    g.lda = lda;
+    g.ldw = ldw;
+    g.ldc = base.ldc;
+    g.ldr = base.ldr;
+    g.act = base.act;
+    g.acc_f16 = base.acc_f16;
+    g.w = w;
+    g.wa = w <= 256 ? w : 32 * ((w + 63) / 64);
+    g.wb = w - g.wa;
+    g.chunks = (g.N + w - 1) / w;
+    g.gemv_rows = wide_gemv_rows(g.M);
+    g.gemv_row0 = g.gemv_rows > 0 ? (g.M / (2 * BM)) * (2 * BM) : g.M;
+    g.stage_bytes = BM * BK * 2 + w * BK;
+    g.stages = WideSmem::stages_for(g.stage_bytes);
+    const int64_t items = wide_row_tiles(g.M) * g.chunks;
+    if (items > 0x3FFFFFFFll) return fail(FBB_ERR_SHAPE, "linear: too many work items (%lld)", (long long)items);
+
+    CUtensorMap ta, twa, twb, tc;
+    uint64_t dims_a[2] = {(uint64_t)g.K, (uint64_t)g.M};
+    int64_t str_a[2] = {1, lda};
+    uint32_t box_a[2] = {BK, BM};
+    int st = make_tmap_f16(&ta, A, 2, dims_a, str_a, box_a);
+    if (st != FBB_OK) return st;
+    uint64_t dims_w[2] = {(uint64_t)g.K, (uint64_t)g.N};
+    int64_t str_w[2] = {1, ldw};
+    uint32_t box_wa[2] = {BK, (uint32_t)(g.wa / 2)};
+    st = make_tmap_f16(&twa, W, 2, dims_w, str_w, box_wa);
+    if (st != FBB_OK) return st;
+    uint32_t box_wb[2] = {BK, (uint32_t)(g.wb > 0 ? g.wb / 2 : g.wa / 2)};
+    st = make_tmap_f16(&twb, W, 2, dims_w, str_w, box_wb);
+    if (st != FBB_OK) return st;
+    uint64_t dims_c[2] = {(uint64_t)g.N, (uint64_t)g.M};
+    int64_t str_c[2] = {1, g.ldc};
+    uint32_t box_c[2] = {32, 32};
+    st = make_tmap_f16(&tc, C, 2, dims_c, str_c, box_c, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (st != FBB_OK) return st;
+
+    cudaError_t e = launch_pdl_cluster(linear_wide_pair_kernel, dim3((unsigned)(2 * items)), dim3(kGemmThreads),
+                                       (size_t)WideSmem::dynamic_bytes(g.stages, g.stage_bytes), stream, 2u, ta, twa, twb, tc, g);
+    if (e != cudaSuccess) return fail((int)e, "linear_wide_pair_kernel launch: %s", cudaGetErrorString(e));
+    return FBB_OK;
+}
+
 static bool gemm_pairs_enabled() {
     static const bool on = []() {
         const char* e = getenv("FBB_GEMM_1CTA");
@@ -407,7 +790,7 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     // operand bytes per FLOP), a pair's tile 0.895 per CTA plus a start-up term for the cluster launch that matters when
     // the per-tile K loop is short (M = 32768, N = 4096, K = 1024: 219 us one-CTA, 196 us pairs; M = 6145: 48 vs 50 us).
     // Pairs with 128-column tiles measured no better than single CTAs and are only reachable through the override.
-    // FBB_GEMM_FORCE = s256 | s128 | p256 | p128 overrides the choice (tuning aid).
+    // FBB_GEMM_FORCE = s256 | s128 | p256 | p128 | w<columns> | wa (the wide form's own width) overrides the choice (tuning aid).
     const int sms = num_sms();
     const bool pairs_ok = gemm_pairs_enabled();
     const int pairs256 = pairs_ok ? (swiglu ? max_pairs<256, true>() : max_pairs<256, false>()) : 0;
@@ -424,13 +807,45 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
         const double c = waves(tm2 * tn256, pairs256) * 0.895 + (K < 1536 ? 0.7 : 0.2);
         if (c < best) { best = c; use_pairs = true; use128 = false; }
     }
+    // The wide pair form (items of w <= 512 columns, one wave): a candidate when every item fits on the device at once with
+    // the narrowest such w and at least half of the pairs get an item. Its cost in the same units: 1.08 per 256 columns
+    // (its epilogue overlaps nothing) plus about 1.8 us of start-up, a unit being one 256-column tile's main loop
+    // (0.37 us per k-block + 1 us). Measured on B200 (us, wide against the best tiled form): M = 6145, N = 1024: K = 4096
+    // 39.6 / 46.0, K = 1024 15.4 / 17.5 (w = 352); M = 4097, N = 768, K = 3072 17.5 / 21.0 (w = 192); not taken where it
+    // measured slower: M = 5480, N = 1536 (w = 512: 25.6 / 22.8), M = 257 (a handful of items), and every shape with
+    // more than one wave of items (N = 4096: 68 / 48).
+    int wide_w = 0;  // > 0: the wide pair form with items of this many columns
+    const int wide_pairs = (pairs_ok && !swiglu) ? wide_max_pairs() : 0;
+    int wide_rule_w = 0;
+    if (wide_pairs > 0) {
+        const int64_t tmw = wide_row_tiles(M);
+        const int64_t max_chunks = tmw > 0 ? wide_pairs / tmw : 0;
+        if (max_chunks >= 1) {
+            int w = (int)(((g.n_out + max_chunks - 1) / max_chunks + 31) / 32 * 32);
+            if (w < 64) w = 64;
+            if (w <= kWideMaxCols && tmw * ((g.n_out + w - 1) / w) <= wide_pairs) wide_rule_w = w;
+        }
+        if (wide_rule_w > 0) {
+            const int64_t items = tmw * ((g.n_out + wide_rule_w - 1) / wide_rule_w);
+            const double unit_us = 0.37 * (double)((K + BK - 1) / BK) + 1.0;
+            const double c = (double)wide_rule_w / 256.0 * 1.08 + 1.8 / unit_us;
+            if (2 * items >= wide_pairs && c < best) wide_w = wide_rule_w;
+        }
+    }
     if (const char* f = getenv("FBB_GEMM_FORCE")) {
+        wide_w = 0;
+        if (f[0] == 'w' && !swiglu && wide_max_pairs() > 0) {
+            const int w = f[1] == 'a' ? wide_rule_w : atoi(f + 1);  // "wa": the rule's own width, whatever the cost model says
+            if (w >= 32 && w <= kWideMaxCols && (w & 31) == 0) wide_w = w;
+        }
         const bool want128 = f[0] != '\0' && f[1] == '1' && !swiglu;  // SwiGLU always uses 256-column tiles (x1 | x2 halves)
         if (f[0] == 's' || (f[0] == 'p' && pairs256 > 0 && (!want128 || max_pairs<128, false>() > 0))) {
             use_pairs = f[0] == 'p';
             use128 = want128;
         }
     }
+
+    if (wide_w > 0) return launch_wide(A, W, C, g, lda, ldw, wide_w, stream);
 
     CUtensorMap ta, tw;
     uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M};

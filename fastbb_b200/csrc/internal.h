@@ -65,6 +65,10 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 int launch_layernorm(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
                      float eps, int in_dtype, int param_dtype, cudaStream_t stream);
 
+// Final norm with split outputs (layernorm.cu): x [B, N, C] fp16 contiguous -> cls / register / patch destinations.
+int launch_layernorm_split(const void* x, const void* w, const void* b, void* patches_out, void* cls_out, void* regs_out, int B, int N, int C,
+                           int n_prefix, float eps, int apply_norm, int channel_major, cudaStream_t stream);
+
 int launch_linear(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M,
                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
                   cudaStream_t stream);

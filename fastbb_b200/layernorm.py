@@ -49,3 +49,33 @@ def module_norm(norm, x, out=None):
     if tuple(norm.normalized_shape) != (x.shape[-1],):
         raise ValueError("only LayerNorm over the last dimension is supported")
     return layer_norm(x, norm.weight, norm.bias, norm.eps, out=out)
+
+
+def layer_norm_split(x, weight=None, bias=None, eps=1e-6, n_prefix=1, grid=None, norm=True):
+    """The final norm of a ViT with its outputs split as get_intermediate_layers returns them, in one launch
+    (kernel: layernorm_split_f16_kernel; replaces vit.norm + cls split + register drop + the permute / contiguous copy of
+    reshape=True, fastbb/vit.py:184,225-232).
+
+    x [B, N, C] fp16 contiguous, rows 0 .. n_prefix-1 of an image = cls + register tokens. Returns (patches, cls, regs):
+    patches [B, N - n_prefix, C], or [B, C, h, w] when grid=(h, w) is given; cls [B, C]; regs [B, n_prefix - 1, C] (None
+    without registers). norm=False copies the rows unnormalised."""
+    if not (x.is_cuda and x.dtype == torch.float16 and x.dim() == 3 and x.is_contiguous()):
+        raise ValueError("layer_norm_split needs a contiguous CUDA fp16 [B, N, C] tensor")
+    B, N, C = x.shape
+    HW = N - n_prefix
+    if grid is not None and grid[0] * grid[1] != HW:
+        raise ValueError(f"grid {tuple(grid)} does not match the {HW} patch tokens")
+    for p in (weight, bias):
+        if p is not None and not (p.numel() == C and p.is_contiguous() and p.device == x.device and p.dtype == torch.float16):
+            raise ValueError("weight / bias must be contiguous fp16 [C] tensors on the input's device")
+    patches = torch.empty((B, C, *grid) if grid is not None else (B, HW, C), device=x.device, dtype=torch.float16)
+    cls = torch.empty((B, C), device=x.device, dtype=torch.float16)
+    regs = torch.empty((B, n_prefix - 1, C), device=x.device, dtype=torch.float16) if n_prefix > 1 else None
+    if B == 0 or N == 0:
+        return patches, cls, regs
+    with _on(x.device):
+        _lib.check(_lib.load().fbb_layernorm_split_f16(
+            x.data_ptr(), _lib.ptr(weight), _lib.ptr(bias), patches.data_ptr(), cls.data_ptr(), _lib.ptr(regs), B, N, C, n_prefix,
+            float(eps), 1 if norm else 0, 1 if grid is not None else 0, _lib.stream_ptr(x.device)))
+    _lib.launched()
+    return patches, cls, regs

@@ -22,9 +22,9 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
-from .attention import _workspace, attention
+from .attention import Workspaces, _workspace, attention, use_workspaces
 from .gemm import linear
-from .layernorm import layer_norm
+from .layernorm import layer_norm, layer_norm_split
 
 HEAD_DIM = 64
 
@@ -205,6 +205,7 @@ class FastViT:
         self._graphs, self._pool, self._graph_version = {}, None, None
         self._orig = {}
         self._patch_w, self._patch_w_version = None, None
+        self._workspaces = Workspaces()  # this instance's attention scratch memory (never shared with another model or graph)
 
     _version = staticmethod(_param_version)
 
@@ -303,14 +304,17 @@ class FastViT:
         return run_block(b, x, self.attn, self.gacc)
 
     # ------------------------------------------------------------------ API
-    def run(self, x, layers, norm=True):
-        """-> list of tokens [B, 1 + nreg + HW, C] after the blocks in `layers` (normed with vit.norm if norm)."""
+    def run(self, x, layers, norm=True, split=False):
+        """-> list of tokens [B, 1 + nreg + HW, C] after the blocks in `layers` (normed with vit.norm if norm).
+        split=True (what get_intermediate_layers(reshape=True) uses): a list of (patches [B, C, h, w], cls [B, C], registers)
+        instead, written by ONE launch per selected layer (final norm + cls split + register drop + channel-major store)
+        when vit.norm is a plain LayerNorm; otherwise the same tuple built with torch ops."""
         out = []
         layers = sorted(l for l in set(layers) if 0 <= l < len(self.blocks))  # as the reference's loop: others never match
         if not layers:
             return out
         last = layers[-1]
-        with torch.autocast("cuda", enabled=False):
+        with torch.autocast("cuda", enabled=False), use_workspaces(self._workspaces):
             t = self.tokens(x).contiguous()
             # One C call per run of blocks between two selected layers (t is this function's own buffer, updated in
             # place); blocks the C runner does not cover, or FBB_NO_RUNNER=1, take the per-operator path.
@@ -322,55 +326,74 @@ class FastViT:
                     use_runner = False
                     for b in self.blocks[i:j + 1]:
                         t = run_block(b, t, self.attn, self.gacc)
-                out.append(_norm(self.vit.norm, t) if norm else t.clone())
+                out.append(self._split_outputs(t, x, norm) if split else (_norm(self.vit.norm, t) if norm else t.clone()))
                 i = j + 1
+        if os.environ.get("FBB_CHECK_STATUS") == "1" and not torch.cuda.is_current_stream_capturing():
+            _lib.device_status()  # debugging aid (synchronises): raises if a kernel of this run gave up a bounded wait
         return out
 
-    def run_graphed(self, x, layers, norm=True):
+    def _split_outputs(self, t, x, norm):
+        """(patches [B, C, h, w], cls, registers) of the token tensor t for an input image batch x."""
+        B, _, h, w = x.shape
+        grid, n_prefix, nm = (h // self.ps, w // self.ps), 1 + self.nreg, self.vit.norm
+        plain = (t.is_cuda and isinstance(nm, torch.nn.LayerNorm) and tuple(nm.normalized_shape) == (t.shape[-1],) and t.shape[-1] <= 2048
+                 and n_prefix <= 32 and all(p is None or (p.dtype == torch.float16 and p.is_contiguous()) for p in (nm.weight, nm.bias)))
+        if plain:
+            return layer_norm_split(t, nm.weight, nm.bias, nm.eps, n_prefix=n_prefix, grid=grid, norm=norm)
+        o = _norm(nm, t) if norm else t
+        patches = o[:, n_prefix:].reshape(B, grid[0], grid[1], -1).permute(0, 3, 1, 2).contiguous()
+        return patches, o[:, 0].clone(), (o[:, 1:n_prefix].clone() if self.nreg else None)
+
+    def run_graphed(self, x, layers, norm=True, split=False):
         """graphs=True: one CUDA graph per (input shape, layers), captured on first use after one warm-up run; outputs
         are the graph's static buffers (cloned unless graph_noclone). Falls back to run() for inference tensors."""
         self._refresh_pos()
         version = _param_version(self.vit.parameters())
         if version is None:
-            return self.run(x, layers, norm)
+            return self.run(x, layers, norm, split)
         if version != self._graph_version:
             self._graphs.clear()
             self._pool = None
             self._graph_version = version
-        key = (tuple(x.shape), x.dtype, x.device, tuple(sorted(layers)), norm)
+        key = (tuple(x.shape), x.dtype, x.device, tuple(sorted(layers)), norm, split)
         entry = self._graphs.get(key)
         if entry is None:
             static_in = x.clone()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.run(static_in, layers, norm)  # warm-up: position cache, kernel attributes
+                self.run(static_in, layers, norm, split)  # warm-up: position cache, kernel attributes, attention workspace
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._pool):
-                static_out = self.run(static_in, layers, norm)
+                static_out = self.run(static_in, layers, norm, split)
             self._pool = graph.pool()
             entry = self._graphs[key] = (graph, static_in, static_out)
         graph, static_in, static_out = entry
         static_in.copy_(x)
         graph.replay()
-        return static_out if self.graph_noclone else [o.clone() for o in static_out]
+        if self.graph_noclone:
+            return static_out
+        return [tuple(None if e is None else e.clone() for e in o) if isinstance(o, tuple) else o.clone() for o in static_out]
 
-    def _run(self, x, layers, norm):
-        return (self.run_graphed if self.graphs else self.run)(x, layers, norm)
+    def _run(self, x, layers, norm, split=False):
+        return (self.run_graphed if self.graphs else self.run)(x, layers, norm, split)
 
     def get_intermediate_layers(self, x, n=1, reshape=False, return_class_token=False, norm=True):
         """Same contract as DinoVisionTransformer.get_intermediate_layers (fastbb/vit.py:220-235)."""
         nb = len(self.blocks)
         layers = list(range(nb - n, nb)) if isinstance(n, int) else list(n)
-        outs = self._run(x, set(layers), norm)
-        if self.out_dtype is not None and self.out_dtype != self.dtype:
-            outs = [o.to(self.out_dtype) for o in outs]
-        cls = [o[:, 0] for o in outs]
-        outs = [o[:, 1 + self.nreg:] for o in outs]
-        if reshape:
-            B, _, h, w = x.shape
-            outs = [o.reshape(B, h // self.ps, w // self.ps, -1).permute(0, 3, 1, 2).contiguous() for o in outs]
+        cast = self.out_dtype is not None and self.out_dtype != self.dtype
+        if reshape:  # [B, C, h, w] patches: one launch per layer does the norm, the cls split and the channel-major store
+            triples = self._run(x, set(layers), norm, split=True)
+            outs = [p.to(self.out_dtype) if cast else p for p, _, _ in triples]
+            cls = [c.to(self.out_dtype) if cast else c for _, c, _ in triples]
+        else:
+            outs = self._run(x, set(layers), norm)
+            if cast:
+                outs = [o.to(self.out_dtype) for o in outs]
+            cls = [o[:, 0] for o in outs]
+            outs = [o[:, 1 + self.nreg:] for o in outs]
         return tuple(zip(outs, cls)) if return_class_token else tuple(outs)
 
     def forward_features(self, x):
@@ -398,9 +421,11 @@ class FastViT:
 class _BlockCfg:
     """Spec of a patched block (attention variant, GEMM accumulate mode)."""
 
-    def __init__(self, attn, gacc):
+    def __init__(self, attn, gacc, workspaces=None):
         _gemm_variants(gacc)
         self.attn, self.gacc = attn, gacc
+        # attention scratch memory shared by the blocks patched in one install_vit_blocks call (they run one after another)
+        self.workspaces = workspaces if workspaces is not None else Workspaces()
 
     def block(self, b, x, own=False):
         """One block on x [B, N, C] fp16 contiguous -> new tensor. `own`: x is a private copy the call may overwrite.
@@ -454,7 +479,7 @@ def _fast_block_forward(self, x, *args, **kw):
         return type(self).forward(self, x, *args, **kw)
     cfg = self._fbb_cfg
     caller_dtype = x.dtype
-    with torch.autocast("cuda", enabled=False):
+    with torch.autocast("cuda", enabled=False), use_workspaces(cfg.workspaces):
         wd = self.attn.qkv.weight.dtype
         xc = x.to(wd).contiguous()
         y = cfg.block(self, xc, own=xc.data_ptr() != x.data_ptr())  # a cast or compaction made a private copy already
@@ -469,11 +494,12 @@ def install_vit_blocks(model, spec="fh-g0", convert=True):
     if convert:
         model.half()
     n = 0
+    workspaces = Workspaces()
     for b in model.modules():
         if b is model and not hasattr(b, "norm1"):
             continue
         if "_fbb_cfg" not in b.__dict__ and _block_supported(b):
-            b._fbb_cfg = _BlockCfg(attn, gacc)
+            b._fbb_cfg = _BlockCfg(attn, gacc, workspaces)
             b.forward = _fast_block_forward.__get__(b)
             n += 1
     return n

@@ -7,12 +7,15 @@
  * Conventions
  *  - every pointer is a device pointer in the caller's current CUDA context/device; nothing is allocated or freed by
  *    the library on any of these calls (the one kernel that wants scratch memory takes it from the caller, see
- *    fbb_flash64_f16_ws), and no call synchronises except fbb_device_status();
+ *    fbb_flash64_f16_ws, or from a device array built into the library, see fbb_flash64_f16_static), and no call
+ *    synchronises except fbb_device_status();
  *  - `stream` is a cudaStream_t passed as void* (0 = legacy default stream); work is only enqueued;
  *  - all leading dimensions and strides are in ELEMENTS, not bytes;
  *  - return value: 0 = success, < 0 = argument rejected on the host before any launch (FBB_ERR_*), > 0 = cudaError_t;
  *    fbb_last_error() gives a thread-local message for the last non-zero status of the calling thread;
- *  - thread-compatible: no mutable state is shared between calls, except a workspace the caller passes to both.
+ *  - thread-compatible: the mutable state shared between calls is (a) a workspace the caller passes to both, (b) the
+ *    built-in device array of fbb_flash64_f16_static, shared by every call of that entry point on a device (calls that
+ *    overlap on the GPU race on it), and (c) a mutex-guarded host table of encoded tensor maps (a pure cache).
  */
 #ifndef FASTBB_B200_H_
 #define FASTBB_B200_H_
@@ -73,6 +76,18 @@ const char* fbb_last_error(void);
  * wait (its output is then undefined), or a cudaError_t. Meant for tests and debugging, never for the hot path. */
 int fbb_device_status(unsigned int out[4]);
 
+/* Diagnostics: launches one warp that waits, with the library's bounded wait and the given limit (nanoseconds, at most
+ * 100 ms), on a barrier nothing ever arrives on. The wait gives up and the kernel returns normally, after recording
+ * {code 5 (other wait), detail, block 0} in the device status word: the next fbb_device_status() returns
+ * FBB_ERR_DEVICE_WAIT with those values and clears them. Exercises the path every pipeline wait of the kernels takes
+ * when it runs out; nothing faults or hangs. No counterpart in the reference. */
+int fbb_diag_wait_timeout(uint64_t limit_ns, unsigned int detail, void* stream);
+
+/* Diagnostics: enqueues a one-thread kernel that counts spin_clocks (1024 .. 2^24) SM clocks against the nanosecond
+ * timer and writes the ratio in MHz to *out_mhz (device memory): the SM clock at that point of the stream, as the
+ * kernels around it see it. No counterpart in the reference. */
+int fbb_diag_sm_clock_mhz(float* out_mhz, int64_t spin_clocks, void* stream);
+
 /* Diagnostics: how many two-CTA clusters of the linear kernel (tile_columns = 128 or 256) the current device can hold at
  * once; 0 means the kernel runs in its one-CTA form. No counterpart in the reference (its GEMMs are cuBLAS calls). */
 int fbb_linear_max_cta_pairs(int tile_columns);
@@ -83,6 +98,17 @@ int fbb_linear_max_cta_pairs(int tile_columns);
  * Requires C % 8 == 0, ldx % 8 == 0 (fp16/bf16) or % 4 (fp32), ldy % 8 == 0, 16-byte aligned pointers. */
 int fbb_layernorm_f16(const void* x, void* y, const void* w, const void* b, int64_t M, int C, int64_t ldx, int64_t ldy,
                       float eps, int in_dtype, int param_dtype, void* stream);
+
+/* The final norm of a ViT with the outputs split as get_intermediate_layers returns them, in one launch.
+ * Replaces: vit.norm followed by the cls split, the register drop and, for reshape=True, the permute + contiguous copy
+ * into [B, C, h, w] (fastbb/vit.py:184,225-232).
+ * x: [B, N, C] fp16 contiguous; row 0 of an image is its cls token, rows 1 .. n_prefix-1 its register tokens, the other
+ * HW = N - n_prefix rows its patch tokens. w, b: [C] fp16 or null. apply_norm = 0 copies the rows unnormalised (norm=False).
+ *   cls_out  [B, C] or null;  regs_out [B, n_prefix-1, C] or null;
+ *   patches_out: channel_major = 0: [B, HW, C] (token-major);  channel_major = 1: [B, C, HW], i.e. [B, C, h, w].
+ * Requires C % 8 == 0, C <= 2048, 1 <= n_prefix <= 32, 16-byte aligned pointers. */
+int fbb_layernorm_split_f16(const void* x, const void* w, const void* b, void* patches_out, void* cls_out, void* regs_out, int B, int N,
+                            int C, int n_prefix, float eps, int apply_norm, int channel_major, void* stream);
 
 /* C[M, Nout] = epilogue(A[M, K] . W[N, K]^T), fp16 operands, tcgen05 tensor cores.
  * Replaces: F.linear / torch._addmm_activation / F.gelu / F.silu.mul_ / addcmul of fastbb/vit.py:114-143, and

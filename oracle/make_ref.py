@@ -1,0 +1,51 @@
+"""Install the reference package (fastforks/fastbb) into oracle/_ref/, which is git-ignored: build output, never history.
+
+    python oracle/make_ref.py [/path/to/reference]          (default: $FASTBB_REFERENCE, then the build container's checkout)
+
+TEST / BENCH INFRASTRUCTURE ONLY. What lands in oracle/_ref/ is the reference's own, unmodified `fastbb` package; only
+bench.py's CPU legs (`--impl reference`, `cpu_baseline`) and tests may import it, to time and check the reference's
+friendly fp32 tier (FastViT(attn="sdpa", gacc=False, dtype=float32), fastbb/vit.py:42,108-150) on the host cores.
+Nothing under fastbb_b200/ imports it. The reference checkout itself does not travel to the GPU machine; this folder,
+like the built .so files, does.
+
+The install is a plain `pip install --no-deps --no-build-isolation --target oracle/_ref` of a temporary copy of the
+checkout (the checkout is read-only and setuptools writes into the source tree). If pip is unavailable the package
+directory is copied instead; either way the result is the same Python files.
+"""
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+DEST = os.path.join(HERE, "_ref")
+DEFAULT_SRC = os.environ.get("FASTBB_REFERENCE", os.path.join(os.sep, "root", "reference"))
+
+
+def available():
+    return os.path.exists(os.path.join(DEST, "fastbb", "vit.py"))
+
+
+def make(src=DEFAULT_SRC, force=False):
+    """Returns DEST if the reference is (now) installed there, None if there is no checkout to install from."""
+    if available() and not force:
+        return DEST
+    if not os.path.exists(os.path.join(src, "fastbb", "vit.py")):
+        return None
+    if os.path.isdir(DEST):
+        shutil.rmtree(DEST)
+    os.makedirs(DEST)
+    with tempfile.TemporaryDirectory() as tmp:
+        copy = os.path.join(tmp, "reference")
+        shutil.copytree(src, copy, ignore=shutil.ignore_patterns(".git", "*.fatbin", "__pycache__"))
+        cmd = [sys.executable, "-m", "pip", "install", "--quiet", "--no-index", "--no-deps", "--no-build-isolation", "--target", DEST, copy]
+        ok = subprocess.run(cmd, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL).returncode == 0 and available()
+        if not ok:
+            shutil.copytree(os.path.join(copy, "fastbb"), os.path.join(DEST, "fastbb"), dirs_exist_ok=True)
+    return DEST if available() else None
+
+
+if __name__ == "__main__":
+    out = make(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_SRC, force=True)
+    print(out or "no reference checkout found: oracle/_ref not made")

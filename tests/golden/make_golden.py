@@ -1,6 +1,10 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself (its friendly fp32 CPU tier).
 
-    python tests/golden/make_golden.py /path/to/reference          (a checkout of fastforks/fastbb; or $FASTBB_REFERENCE)
+    python tests/golden/make_golden.py /path/to/reference [fixture ...]     (a checkout of fastforks/fastbb; or $FASTBB_REFERENCE)
+
+Without fixture names every fixture is regenerated (the results are deterministic: same seeds, same bits); with names
+(c0_vits14_224, c1_vitl14_896x1344, c3_vitg14_518, c3_vitg14_518_b4, c2_vitb16_blocks_1025, c2_vitb16_blocks_4097_b8, ops)
+only those.
 
 The reference is a Python package whose fp32 tier needs no GPU: FastViT(attn="sdpa", gacc=False, dtype=float32)
 (fastbb/vit.py:42,108-150), install_vit_blocks(model, "sdpa-g0", convert=False) (fastbb/vit.py:311-328), gemm.linear
@@ -25,6 +29,7 @@ STACKS = [
     ("c0_vits14_224", "vits14", 224, 224, 1, [2, 5, 8, 11], 2),
     ("c1_vitl14_896x1344", "vitl14", 896, 1344, 1, [4, 11, 17, 23], 128),
     ("c3_vitg14_518", "vitg14", 518, 518, 1, [9, 19, 29, 39], 32),
+    ("c3_vitg14_518_b4", "vitg14", 518, 518, 4, [9, 19, 29, 39], 64),   # the per-GPU share of batch 32 on eight GPUs
 ]
 PARAM_SEED, IMAGE_SEED = 0, 1
 OP_STRIDE = 4  # operator outputs are stored every 4th row / token
@@ -63,7 +68,8 @@ def timm_like_stack(ref_dinov2, depth=12, d=768, heads=12):
     return Stack()
 
 
-def main(ref_root):
+def main(ref_root, only=()):
+    want = lambda name: not only or name in only  # noqa: E731
     sys.path.insert(0, ref_root)
     import fastbb  # the reference
     from fastbb import attention as ref_attention
@@ -73,6 +79,8 @@ def main(ref_root):
 
     torch.manual_seed(0)
     for name, arch, H, W, B, layers, stride in STACKS:
+        if not want(name):
+            continue
         params = O.make_params(arch, seed=PARAM_SEED)
         x = O.make_image(B, H, W, seed=IMAGE_SEED)
         m = ref_dinov2.DinoV2Params(arch)
@@ -88,6 +96,8 @@ def main(ref_root):
             rec[f"patch_{i}"] = patch[:, ::stride].numpy().astype(np.float32)
             rec[f"cls_{i}"] = cls.numpy().astype(np.float32)
             rec[f"patch_norm_{i}"] = np.array(float(patch.double().norm()))
+            if B > 1:
+                rec[f"patch_norm_per_image_{i}"] = patch.double().flatten(1).norm(dim=1).numpy()
         np.savez(os.path.join(HERE, name + ".npz"), **rec)
         print(name, {k: getattr(v, "shape", None) for k, v in rec.items() if k.startswith("patch_") and "norm" not in k})
 
@@ -99,12 +109,24 @@ def main(ref_root):
     stack.eval()
     n = fastbb.install_vit_blocks(stack, "sdpa-g0", convert=False)
     assert n == 12, n
-    tokens = torch.randn(1, 1025, 768, generator=torch.Generator().manual_seed(IMAGE_SEED))  # 512x512 / 16 + cls
-    with torch.no_grad():
-        y = stack(tokens)
-    np.savez(os.path.join(HERE, "c2_vitb16_blocks_1025.npz"), out=y[:, ::16].numpy().astype(np.float32),
-             out_norm=np.array(float(y.double().norm())), token_stride=np.array(16), tokens_checksum=np.array(checksum(tokens)))
-    print("c2_vitb16_blocks_1025", tuple(y.shape))
+    if want("c2_vitb16_blocks_1025"):
+        tokens = torch.randn(1, 1025, 768, generator=torch.Generator().manual_seed(IMAGE_SEED))  # 512x512 / 16 + cls
+        with torch.no_grad():
+            y = stack(tokens)
+        np.savez(os.path.join(HERE, "c2_vitb16_blocks_1025.npz"), out=y[:, ::16].numpy().astype(np.float32),
+                 out_norm=np.array(float(y.double().norm())), token_stride=np.array(16), tokens_checksum=np.array(checksum(tokens)))
+        print("c2_vitb16_blocks_1025", tuple(y.shape))
+    if want("c2_vitb16_blocks_4097_b8"):
+        # the configuration as stated: 1024x1024 / 16 + cls = 4097 tokens, batch 8 (batch 1 = its first image)
+        tokens = torch.randn(8, 4097, 768, generator=torch.Generator().manual_seed(IMAGE_SEED))
+        with torch.no_grad():
+            y = torch.cat([stack(tokens[i:i + 1]) for i in range(8)])
+        np.savez(os.path.join(HERE, "c2_vitb16_blocks_4097_b8.npz"), out=y[:, ::128].numpy().astype(np.float32),
+                 out_norm_per_image=y.double().flatten(1).norm(dim=1).numpy(), token_stride=np.array(128),
+                 tokens_checksum=np.array(checksum(tokens)))
+        print("c2_vitb16_blocks_4097_b8", tuple(y.shape))
+    if not want("ops"):
+        return
 
     # ---- operators: the reference's gemm.linear and attention.attention on CPU tensors
     g = torch.Generator().manual_seed(7)
@@ -139,4 +161,4 @@ if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FASTBB_REFERENCE")
     if not ref:
         sys.exit("usage: make_golden.py /path/to/reference  (a checkout of fastforks/fastbb)")
-    main(ref)
+    main(ref, tuple(sys.argv[2:]))

@@ -75,6 +75,52 @@ def test_layernorm_strided_rows_and_errors(oracle):
     assert layer_norm(torch.zeros(0, 64, dtype=torch.float16, device=dev())).shape == (0, 64)
 
 
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("B,N,C,n_prefix,grid", [(2, 257, 384, 1, (16, 16)), (1, 6145, 1024, 1, (64, 96)), (2, 105, 384, 5, (10, 10)),
+                                                 (3, 1370, 1536, 1, (37, 37)), (1, 40, 2048, 3, (1, 37)), (2, 2, 64, 1, (1, 1))])
+def test_layernorm_split_matches_oracle_in_both_layouts(oracle, B, N, C, n_prefix, grid, norm):
+    """The final norm with split outputs: cls rows, register rows and patch rows (token-major, and channel-major =
+    [B, C, h, w]) against the oracle's LayerNorm of the same rows; the channel-major tensor is the token-major one
+    transposed, bit for bit, and both equal the plain LayerNorm kernel's output (bit for bit where that kernel uses the
+    same arithmetic)."""
+    from fastbb_b200.layernorm import layer_norm, layer_norm_split
+    g = torch.Generator().manual_seed(B * 7 + N + C)
+    x = (torch.randn(B, N, C, generator=g) * 1.5 + 0.3).half()
+    w, b = (1 + 0.1 * torch.randn(C, generator=g)).half(), (0.1 * torch.randn(C, generator=g)).half()
+    xd, wd, bd = x.to(dev()), w.to(dev()), b.to(dev())
+    p_tok, cls, regs = layer_norm_split(xd, wd, bd, 1e-6, n_prefix=n_prefix, norm=norm)
+    p_chw, cls2, regs2 = layer_norm_split(xd, wd, bd, 1e-6, n_prefix=n_prefix, grid=grid, norm=norm)
+    want = oracle.layer_norm(x, w, b, 1e-6) if norm else x.float()
+    assert p_tok.shape == (B, N - n_prefix, C) and p_chw.shape == (B, C, *grid) and p_chw.is_contiguous()
+    assert oracle.rel_l2(p_tok.cpu().float(), want[:, n_prefix:]) < TOL_F32
+    assert oracle.rel_l2(cls.cpu().float(), want[:, 0]) < TOL_F32
+    assert torch.equal(p_chw.flatten(2).transpose(1, 2), p_tok) and torch.equal(cls, cls2)
+    if n_prefix > 1:
+        assert regs.shape == (B, n_prefix - 1, C) and torch.equal(regs, regs2)
+        assert oracle.rel_l2(regs.cpu().float(), want[:, 1:n_prefix]) < TOL_F32
+    else:
+        assert regs is None
+    full = layer_norm(xd, wd, bd, 1e-6) if norm else xd
+    if C <= 1536:  # rows this short take the two-rows-per-warp kernel, whose arithmetic the split kernel repeats exactly
+        assert torch.equal(p_tok, full[:, n_prefix:]) and torch.equal(cls, full[:, 0])
+    else:
+        assert oracle.rel_l2(p_tok.float(), full[:, n_prefix:].float()) < 3e-4
+    status_ok()
+
+
+def test_layernorm_split_rejects_what_it_does_not_cover():
+    from fastbb_b200 import _lib
+    from fastbb_b200.layernorm import layer_norm_split
+    x = torch.zeros(1, 50, 64, dtype=torch.float16, device=dev())
+    with pytest.raises(ValueError):
+        layer_norm_split(x, grid=(7, 8))                      # 56 != 49 patch tokens
+    with pytest.raises(_lib.FastbbError):
+        layer_norm_split(x, n_prefix=40)                      # more prefix rows than the kernel's one prefix tile holds
+    with pytest.raises(ValueError):
+        layer_norm_split(x.float())
+    assert layer_norm_split(x[:0])[0].shape == (0, 49, 64)
+
+
 # ------------------------------------------------------------------------------------------------ linear
 LINEAR_CASES = [
     # M, N, K, act, bias, res, variant
@@ -117,10 +163,12 @@ def test_linear_matches_oracle(oracle, M, N, K, act, has_bias, has_res, variant)
     status_ok()
 
 
-@pytest.mark.parametrize("form", ["s256", "s128", "p256", "p128"])
+@pytest.mark.parametrize("form", ["s256", "s128", "p256", "p128", "w32", "w96", "w256", "w288", "w352", "w512"])
 def test_linear_every_tile_form_matches_oracle(oracle, form, monkeypatch):
-    """The kernel has four forms (one CTA or a CTA pair per tile, 256- or 128-column tiles) and picks one by a cost
-    model; this forces each of them on tail-heavy shapes, including the SwiGLU and fp16-accumulate epilogues."""
+    """The kernel has several forms (one CTA or a CTA pair per tile, 256- or 128-column tiles; wide pair items of 32 to
+    512 columns over two accumulators, with the rows beyond the last full 256-row tile computed by the epilogue warps)
+    and picks one by a cost model; this forces each of them on tail-heavy shapes, including the SwiGLU (which never
+    takes the wide form and falls through to the default choice) and fp16-accumulate epilogues."""
     from fastbb_b200 import _lib
     from fastbb_b200.gemm import linear
     monkeypatch.setenv("FBB_GEMM_FORCE", form)
@@ -128,7 +176,7 @@ def test_linear_every_tile_form_matches_oracle(oracle, form, monkeypatch):
         pytest.skip("this device cannot co-schedule CTA pairs")
     g = torch.Generator().manual_seed(99)
     for M, N, K, act, variant in [(513, 1160, 200, "gelu", "f32"), (257, 384, 1536, None, "f32"), (1370, 1024, 264, "swiglu", "f32"),
-                                  (300, 520, 72, None, "h"), (1, 256, 64, None, "f32")]:
+                                  (300, 520, 72, None, "h"), (1, 256, 64, None, "f32"), (264, 200, 136, "gelu", "h"), (776, 72, 64, None, "f32")]:
         x = torch.randn(M, K, generator=g).half()
         w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
         b = (0.1 * torch.randn(N, generator=g)).half()
@@ -225,6 +273,40 @@ def test_linear_full_size_linearity_and_column_sums(M, N, K):
     status_ok()
 
 
+def _sample_rows(M, tile=128, n_random=24, seed=0):
+    """First and last rows, both sides of a few tile boundaries, the ragged last tile, and some seeded random rows."""
+    rows = {0, 1, tile - 1, tile, 2 * tile - 1, 2 * tile, M // 2, M - 1, M - 2, (M - 1) // tile * tile, (M - 1) // tile * tile - 1,
+            (M - 1) // (2 * tile) * (2 * tile), (M - 1) // (2 * tile) * (2 * tile) - 1}
+    g = torch.Generator().manual_seed(seed)
+    rows |= set(int(i) for i in torch.randint(0, M, (n_random,), generator=g))
+    return sorted(r for r in rows if 0 <= r < M)
+
+
+@pytest.mark.parametrize("variant", ["f32", "h"])
+@pytest.mark.parametrize("M", [6145, 32768])
+@pytest.mark.parametrize("K,N,act,has_res", [(1024, 3072, None, False), (1024, 1024, None, True), (1024, 4096, "gelu", False),
+                                             (4096, 1024, None, True), (1024, 4096, "swiglu", False)])
+def test_linear_full_size_sampled_rows_match_oracle(oracle, M, K, N, act, has_res, variant):
+    """Benchmark-size GEMMs against the oracle on a sample of output rows (every column of each): real values, not only
+    invariants, at the sizes where the tile forms, tail waves and the remainder rows differ from the small cases."""
+    from fastbb_b200.gemm import linear
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device=dev(), generator=g).half()
+    w = (torch.randn(N, K, device=dev(), generator=g) * 0.02).half()
+    b = (torch.randn(N, device=dev(), generator=g) * 0.1).half()
+    n_out = N // 2 if act == "swiglu" else N
+    res = torch.randn(M, n_out, device=dev(), generator=g).half() if has_res else None
+    gam = (0.05 + 0.15 * torch.rand(n_out, device=dev(), generator=g)).half() if has_res else None
+    out, check = padded((M, n_out))
+    y = linear(x, w, b, act=act, res=res, gamma=gam, variant=variant, out=out)
+    rows = _sample_rows(M, seed=N)
+    want = oracle.linear(x[rows].cpu(), w.cpu(), b.cpu(), act=act, res=None if res is None else res[rows].cpu(),
+                         gamma=None if gam is None else gam.cpu())
+    assert oracle.rel_l2(y[rows].cpu().float(), want) < (TOL_F16 if variant == "h" else TOL_F32)
+    check()
+    status_ok()
+
+
 # ------------------------------------------------------------------------------------------------ flash attention
 FLASH_SHAPES = [(1, 1, 1), (1, 63, 2), (1, 64, 2), (1, 65, 1), (1, 127, 3), (1, 128, 1), (1, 129, 2), (1, 257, 6), (2, 400, 16),
                 (1, 1370, 16), (3, 255, 5)]
@@ -295,6 +377,25 @@ def test_flash_full_size_properties(variant, N):
     status_ok()
 
 
+@pytest.mark.parametrize("variant", ["ff", "fh", "hh"])
+@pytest.mark.parametrize("B,N,H", [(1, 4097, 16), (1, 6145, 16), (1, 16385, 16), (8, 4097, 12), (4, 1370, 24)])
+def test_flash_full_size_sampled_rows_match_oracle(oracle, variant, B, N, H):
+    """Benchmark-size sequences against the oracle on a sample of query rows against ALL keys (first and last rows, tile
+    boundaries, the ragged last tile, random rows): pins real values where the invariants above would let a
+    permutation-invariant, row-sum-preserving error through."""
+    from fastbb_b200.attention import attention
+    g = torch.Generator(device="cuda").manual_seed(N + H)
+    qkv = torch.randn(B, N, 3, H, 64, device=dev(), generator=g).half()
+    q, k, v = qkv.unbind(2)
+    out, check = padded((B, N, H, 64))
+    o = attention(q, k, v, scale=0.125, variant=variant, out=out)
+    rows = _sample_rows(N, seed=H)
+    want = oracle.attention(q[:, rows].cpu(), k.cpu(), v.cpu(), scale=0.125)
+    assert oracle.rel_l2(o[:, rows].cpu().float(), want) < TOL_F32
+    check()
+    status_ok()
+
+
 @pytest.mark.parametrize("variant", ["ff", "hh"])
 @pytest.mark.parametrize("B,N,H", [(2, 2500, 11), (1, 4097, 12), (20, 300, 16), (1, 6145, 16), (5, 1370, 16)])
 def test_flash_split_form_matches_one_cta_per_group(oracle, variant, B, N, H):
@@ -347,7 +448,36 @@ def test_flash_rejects_what_the_kernel_does_not_cover():
     assert attention(q[:, :0], q[:, :0], q[:, :0]).shape == (1, 0, 2, 64)
 
 
-def test_device_wait_limit_reports_instead_of_hanging():
-    """A clean device reports (0, 0, 0, 0); the status call is the only synchronising entry point."""
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(oracle):
+    """Every pipeline wait in the kernels is bounded: when one runs out, the kernel records a code in the device status
+    word and returns. fbb_diag_wait_timeout runs exactly that wait (same function, a 1 ms limit) on a barrier nothing
+    arrives on; the kernel gives up and returns normally, fbb_device_status reports FBB_ERR_DEVICE_WAIT with the code and
+    detail, clears the word, and the next kernels run clean. Nothing faults, traps or spins past the limit."""
+    import ctypes
     from fastbb_b200 import _lib
+    from fastbb_b200.layernorm import layer_norm
+    lib = _lib.load()
+    assert _lib.device_status() == (0, 0, 0, 0)             # a clean device reports zeros
+    _lib.check(lib.fbb_diag_wait_timeout(1_000_000, 77, _lib.stream_ptr(dev())))
+    out = (ctypes.c_uint * 4)()
+    rc = lib.fbb_device_status(ctypes.byref(out))
+    assert rc == -6 and tuple(out) == (5, 77, 0, 1)          # FBB_ERR_DEVICE_WAIT: other wait, detail, block 0, one report
+    assert b"device wait ran out" in lib.fbb_last_error()
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(lib.fbb_diag_wait_timeout(1_000_000, 78, _lib.stream_ptr(dev())))
+        _lib.device_status()                                 # the Python wrapper turns the status into an exception
+    assert _lib.device_status() == (0, 0, 0, 0)             # cleared by the read
+    x = torch.randn(64, 384, generator=torch.Generator().manual_seed(1)).half()
+    y = layer_norm(x.to(dev()), None, None, 1e-6)            # the context is intact: the next kernel runs and is right
+    assert oracle.rel_l2(y.cpu().float(), oracle.layer_norm(x, None, None, 1e-6)) < TOL_F32
+    with pytest.raises(_lib.FastbbError):
+        _lib.check(lib.fbb_diag_wait_timeout(0, 0, None))    # limits outside (0, 100 ms] are rejected on the host
     assert _lib.device_status() == (0, 0, 0, 0)
+
+
+def test_sm_clock_probe_reads_a_plausible_clock():
+    from fastbb_b200 import _lib
+    buf = torch.zeros(1, dtype=torch.float32, device=dev())
+    _lib.check(_lib.load().fbb_diag_sm_clock_mhz(buf.data_ptr(), 1 << 16, _lib.stream_ptr(dev())))
+    torch.cuda.synchronize()
+    assert 100.0 < float(buf[0]) < 3000.0

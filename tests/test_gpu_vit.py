@@ -21,10 +21,10 @@ def _fast_model(oracle, arch, spec, **kw):
     return params, dinov2(arch, params, spec=spec, device="cuda:0")
 
 
-def _check_against_golden(oracle, name, arch, H, W, heads, spec):
+def _check_against_golden(oracle, name, arch, H, W, heads, spec, batch=1):
     g = load_golden(name)
     params, fast = _fast_model(oracle, arch, spec)
-    x = oracle.make_image(1, H, W, seed=1)
+    x = oracle.make_image(batch, H, W, seed=1)
     assert_same_inputs(g["image_checksum"], x, "image")
     assert_same_inputs(g["qkv0_checksum"], params["blocks.0.attn.qkv.weight"], "qkv weight")
     layers = [int(i) for i in g["layers"]]
@@ -40,8 +40,14 @@ def _check_against_golden(oracle, name, arch, H, W, heads, spec):
         # patch embeddings and is built almost entirely from accumulated block outputs, so the same absolute error is
         # a larger relative one (measured: 2.3e-2 after 40 ViT-g blocks with fp16 accumulators): loose sanity bound only.
         assert e < TOL[spec] and ec < 4 * TOL[spec], f"{name} {spec} layer {i}: patch {e:.2e} cls {ec:.2e}"
-        # whole-tensor norm (all tokens, not just the stored subsample)
+        # whole-tensor norm (all tokens, not just the stored subsample), and per image for batched fixtures
         assert abs(float(patch.double().norm()) / float(g[f"patch_norm_{i}"]) - 1) < TOL[spec]
+        if batch > 1:
+            per_image = patch.double().flatten(1).norm(dim=1).cpu()
+            assert torch.all((per_image / torch.from_numpy(g[f"patch_norm_per_image_{i}"]) - 1).abs() < TOL[spec])
+            for bi in range(batch):  # each image of the batch on its own, against the reference's output for that image
+                eb = oracle.rel_l2(patch[bi:bi + 1, ::stride].float().cpu(), torch.from_numpy(g[f"patch_{i}"][bi:bi + 1]))
+                assert eb < TOL[spec], f"{name} {spec} layer {i} image {bi}: patch {eb:.2e}"
     from fastbb_b200 import _lib
     assert _lib.device_status() == (0, 0, 0, 0)
     return errs
@@ -60,6 +66,13 @@ def test_c1_vitl14_896x1344(oracle, spec):
 @pytest.mark.parametrize("spec", ["hh-g1", "fh-g0"])
 def test_c3_vitg14_518_swiglu(oracle, spec):
     _check_against_golden(oracle, "c3_vitg14_518", "vitg14", 518, 518, 24, spec)
+
+
+@pytest.mark.parametrize("spec", ["hh-g1", "hh-g1-graph"])
+def test_c3_vitg14_518_batch4_the_per_gpu_share_of_batch_32(oracle, spec):
+    """The configuration as it runs on each of eight GPUs: four 518x518 images (5480 tokens in every GEMM, 96 (batch,
+    head) pairs in the attention), against the reference's fp32 output for the same four seeded images."""
+    _check_against_golden(oracle, "c3_vitg14_518_b4", "vitg14", 518, 518, 24, spec, batch=4)
 
 
 def test_c0_against_live_oracle_with_batch_and_odd_grid(oracle):
@@ -110,6 +123,79 @@ def test_graph_replay_equals_eager_and_tracks_weight_reloads(oracle):
         eager.vit.blocks[0].ls1.gamma.mul_(0.5)
     d = graphed.get_intermediate_layers(x2, n=[1, 3])
     assert torch.equal(d[0], eager.get_intermediate_layers(x2, n=[1, 3])[0]) and not torch.equal(d[0], c[0])
+
+
+def test_graphed_wrapper_replays_equal_eager_and_bounds_its_graphs(oracle):
+    """graphs.graphed around any callable built on these kernels (here: attention on a split-form shape, a fused linear
+    and a LayerNorm): replay equals the eager result bit for bit, one graph per input signature, never more than
+    max_graphs held, the attention scratch memory belongs to the wrapper and exists before the capture."""
+    from fastbb_b200.attention import attention
+    from fastbb_b200.gemm import linear
+    from fastbb_b200.graphs import Graphed, graphed
+    from fastbb_b200.layernorm import layer_norm
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(12)
+    w = (torch.randn(3 * 704, 704, generator=g) / 26).half().to(dev)
+
+    def fn(x):
+        B, N, C = x.shape
+        qkv = linear(layer_norm(x, None, None, 1e-6), w).view(B, N, 3, C // 64, 64)
+        q, k, v = qkv.unbind(2)
+        return attention(q, k, v, variant="fh").view(B, N, C)
+
+    f = graphed(fn, max_graphs=2)
+    assert isinstance(f, Graphed)
+    xs = [torch.randn(2, n, 704, generator=g).half().to(dev) for n in (2500, 300, 2500, 777)]
+    for x in xs:
+        want = fn(x)
+        got = f(x)
+        again = f(x)                                         # replay
+        assert torch.equal(got, want) and torch.equal(again, want)
+        assert len(f._entries) <= 2
+    assert len(f._entries) == 1                              # the fourth signature evicted the first two
+    assert f._workspaces._by_device                          # the split form ran from the wrapper's own scratch memory
+    x2 = torch.randn(2, 777, 704, generator=g).half().to(dev)   # same signature, new content: same graph, new result
+    assert torch.equal(f(x2), fn(x2)) and len(f._entries) == 1
+    from fastbb_b200 import _lib
+    assert _lib.device_status() == (0, 0, 0, 0)
+
+
+def test_two_models_captured_one_after_the_other_do_not_share_attention_scratch(oracle):
+    """Each FastViT owns its attention workspace, created in the warm-up run before its graph is captured: two graphed
+    models (even of the same shape) bake in different memory."""
+    from fastbb_b200.models.dinov2 import dinov2
+    params = oracle.make_params("vits14", seed=0, depth=2)
+    a = dinov2("vits14", params, spec="fh-g0-graph", device="cuda:0")
+    b = dinov2("vits14", params, spec="fh-g0-graph", device="cuda:0")
+    xa = oracle.make_image(30, 224, 224, seed=2).to("cuda:0")    # 30 x 6 x 2 = 360 tile groups on 148 SMs: the split form
+    for m in (a, b):
+        m.get_intermediate_layers(xa, n=1)
+    wa, wb = a._workspaces._by_device, b._workspaces._by_device
+    if wa:  # the split form was used on this device
+        assert wb and next(iter(wa.values())).data_ptr() != next(iter(wb.values())).data_ptr()
+    assert torch.equal(a.get_intermediate_layers(xa, n=1)[0], b.get_intermediate_layers(xa, n=1)[0])
+
+
+@pytest.mark.parametrize("spec", ["fh-g0", "hh-g1-graph"])
+def test_reshape_true_runs_the_fused_final_norm_and_equals_the_token_major_path(oracle, spec):
+    """get_intermediate_layers(reshape=True) writes [B, C, h, w] patches, cls and registers with one launch per layer (final
+    norm + split + channel-major store): same bits as the token-major path permuted, against the oracle on c0-sized
+    inputs with registers, and one launch fewer kernels than LayerNorm + torch permute."""
+    from fastbb_b200 import _lib
+    params, fast = _fast_model(oracle, "vits14", spec, num_register_tokens=4, depth=3)
+    x = oracle.make_image(2, 518, 518, seed=11)
+    xd = x.to("cuda:0")
+    a = fast.get_intermediate_layers(xd, n=[0, 2], reshape=True, return_class_token=True)
+    b = fast.get_intermediate_layers(xd, n=[0, 2], reshape=False, return_class_token=True)
+    want = oracle.run(params, x, {0, 2}, 6, norm=True, interpolate_offset=0.0)
+    for (pa, ca), (pb, cb), wt in zip(a, b, want):
+        assert pa.shape == (2, 384, 37, 37) and pa.is_contiguous() and ca.shape == (2, 384)
+        assert torch.equal(pa.flatten(2).transpose(1, 2), pb) and torch.equal(ca, cb)
+        assert oracle.rel_l2(pb.float().cpu(), wt[:, 5:]) < TOL[spec.replace("-graph", "")]
+    raw = fast.get_intermediate_layers(xd, n=1, reshape=True, norm=False)[0]
+    raw_tok = fast.get_intermediate_layers(xd, n=1, norm=False)[0]
+    assert torch.equal(raw.flatten(2).transpose(1, 2), raw_tok)
+    assert _lib.device_status() == (0, 0, 0, 0)
 
 
 def test_install_vit_patches_a_dinov2_style_module(oracle):
@@ -182,6 +268,30 @@ def test_c2_timm_like_block_stack(oracle, spec, batch):
     for bi in range(batch):
         assert oracle.rel_l2(y[bi:bi + 1, ::int(g["token_stride"])].cpu(), torch.from_numpy(g["out"])) < TOL[spec]
     assert abs(float(y[0].double().norm()) / float(g["out_norm"]) - 1) < TOL[spec]
+
+
+@pytest.mark.parametrize("batch", [1, 8])
+def test_c2_timm_like_block_stack_at_4097_tokens(oracle, batch):
+    """The configuration as stated: 1024x1024 / 16 + cls = 4097 tokens, batches 1 and 8, spec fh-g1 through
+    install_vit_blocks, against the reference's own install_vit_blocks(..., "sdpa-g0", convert=False) output on the same
+    seeded tokens (batch 1 is the first image of the batch-8 fixture)."""
+    import fastbb_b200 as fb
+    g = load_golden("c2_vitb16_blocks_4097_b8")
+    params = oracle.make_params("vitb16_timm", seed=0, layerscale=False, patch_size=16, img_size=224)
+    stack = TimmLikeStack()
+    stack.load_state_dict({k: v for k, v in params.items() if k.startswith("blocks.")}, strict=True)
+    stack = stack.to("cuda:0").eval()
+    assert fb.install_vit_blocks(stack, "fh-g1") == 12
+    tokens = torch.randn(8, 4097, 768, generator=torch.Generator().manual_seed(1))
+    assert_same_inputs(g["tokens_checksum"], tokens, "tokens")
+    y = stack(tokens[:batch].to("cuda:0"))
+    assert y.dtype == torch.float32 and y.shape == (batch, 4097, 768)
+    s = int(g["token_stride"])
+    for bi in range(batch):
+        assert oracle.rel_l2(y[bi:bi + 1, ::s].cpu(), torch.from_numpy(g["out"][bi:bi + 1])) < TOL["fh-g1"], bi
+        assert abs(float(y[bi].double().norm()) / float(g["out_norm_per_image"][bi]) - 1) < TOL["fh-g1"]
+    from fastbb_b200 import _lib
+    assert _lib.device_status() == (0, 0, 0, 0)
 
 
 def test_host_pipeline_matches_direct_calls(oracle):

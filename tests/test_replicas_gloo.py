@@ -38,6 +38,8 @@ def _worker(rank, world, port, out):
     replicas.barrier()
     slowest = replicas.max_over_ranks(1.0 + rank)            # rank 1 is the slow one
     total = replicas.sum_over_ranks(float(mine.shape[0]))
+    per_rank = replicas.gather_over_ranks(10.0 * (rank + 1))
+    assert per_rank == [10.0, 20.0]
     gathered = [torch.zeros(3, 2, dtype=batch.dtype) for _ in range(world)]
     pad = torch.zeros(3, 2, dtype=batch.dtype)
     pad[: mine.shape[0]] = mine
@@ -65,3 +67,4 @@ def test_two_gloo_ranks_shard_and_reduce():
 def test_single_process_helpers_are_identities():
     assert replicas.env_rank_world() == (0, 0, 1) or "RANK" in os.environ
     assert replicas.max_over_ranks(3.5) == 3.5 and replicas.sum_over_ranks(2.0) == 2.0
+    assert replicas.gather_over_ranks(1.25) == [1.25]
