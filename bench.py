@@ -14,9 +14,10 @@ Prints ONE JSON line on rank 0.
              downloads its features inside the timed region, on copy streams overlapped with compute; with the per-rank
              times and, for context, each rank's pinned-copy bandwidth measured with all ranks copying at once
   roofline   the dominant kernel (flash attention): algorithmic FLOPs per launch / mean launch time, timed live with CUDA
-             events around each of its launches in a separate instrumented eager pass, against the measured BURST cuBLAS
-             rate (that pass is short); beside it the SM clock the launches ran at (an on-device probe) and the same
-             launch timed alone in this process, so that a difference between the two is explained by the clock or not
+             events around each of its launches in a separate instrumented pass (the per-operator path captured into a
+             graph and replayed back to back), against the measured BURST cuBLAS rate; beside it the SM clock the launches
+             ran at (an on-device probe) and the same launch timed alone in this process, so that a difference between
+             the two is explained by the clock or not
   kernel_ms  the instrumented pass's per-step time in each kernel class and what a step spends outside them (gap_ms)
   configs    the batched configurations split over the ranks (ViT-g/14 batch 32, ViT-B/16 batch 8; at N = 1 their
              eight-GPU share), device-resident and end to end
@@ -189,7 +190,7 @@ def run_ours(args, rank, local_rank, world):
     import torch
     from fastbb_b200 import _lib, replicas
     from fastbb_b200 import vit as vit_mod
-    from fastbb_b200.attention import attention
+    from fastbb_b200.attention import Workspaces, attention, use_workspaces
     from fastbb_b200.models.dinov2 import dinov2
     from fastbb_b200 import synthetic as O
 
@@ -235,16 +236,26 @@ def run_ours(args, rank, local_rank, world):
     probe(0, 1 << 16)          # after the closing event: the SM clock the last steps ran at
     torch.cuda.synchronize()
     replicas.barrier()
-    ms_total = replicas.max_over_ranks(e0.elapsed_time(e1), dev)
+    ms_total_ranks = replicas.gather_over_ranks(e0.elapsed_time(e1), dev)
+    ms_total = max(ms_total_ranks)
     clocks = sampler.summary()
     clocks["sm_mhz_on_device_after_timed_steps"] = round(float(mhz[0]), 1)
+    if world > 1:  # every rank's own GPU: a GPU that the machine slows down shows here, not in rank 0's sampler
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        code = sum(1 << i for i, n in enumerate(names) if n in clocks["reasons"])
+        codes = replicas.gather_over_ranks(code, dev)
+        clocks["per_rank"] = {"ms_per_step": [round(t / args.steps, 3) for t in ms_total_ranks],
+                              "sm_mhz_sampled": [round(v) for v in replicas.gather_over_ranks(clocks["sm_mhz"] or 0.0, dev)],
+                              "sm_mhz_on_device_after_timed_steps": [round(v) for v in replicas.gather_over_ranks(float(mhz[0]), dev)],
+                              "reasons": [[n for i, n in enumerate(names) if int(c) >> i & 1] for c in codes]}
+        clocks["reasons"] = sorted({n for r in clocks["per_rank"]["reasons"] for n in r})
 
     # ---------------- end to end: pinned host image in, pinned host features out, every step's copies inside the timing.
     # Through the package's HostPipeline: uploads and downloads run on side streams, overlapped with the next / previous
     # step's compute (each step still uploads its own image and downloads its own features).
     from fastbb_b200.pipeline import HostPipeline
     pipe = HostPipeline(step, device=dev, depth=3)
-    for _ in range(3):
+    for _ in range(8):  # enough submissions for the allocator to hold every buffer the steady state keeps in flight
         pipe.submit(x_host)
     pipe.drain()
     torch.cuda.synchronize()
@@ -265,49 +276,72 @@ def run_ours(args, rank, local_rank, world):
     bw_h2d, bw_d2h = copy_bandwidth(dev)
     bw_h2d_ranks, bw_d2h_ranks = replicas.gather_over_ranks(bw_h2d, dev), replicas.gather_over_ranks(bw_d2h, dev)
 
-    # ---------------- instrumented eager pass: events around every launch of the three kernel classes, the clock after
-    # every attention launch. The per-operator host path (same kernels, same order as the C stack runner) so that each
-    # launch can be bracketed.
+    # ---------------- instrumented pass: events around every launch of the three kernel classes, the SM clock after every
+    # fourth attention launch. The per-operator host path (same kernels, same order as the C stack runner) is captured into
+    # one CUDA graph with an (external) event on either side of each launch, and that graph is replayed back to back like
+    # the timed steps: the times are device times without host gaps, in the clock regime the timed steps run in. The
+    # event nodes keep a kernel's set-up from overlapping the previous kernel's tail, so the per-class sums are upper
+    # bounds (gap_ms comes out near zero or slightly negative). Where external events are not available the same
+    # brackets are taken in eager mode, which adds launch latency to every launch.
     variant = "ff" if fast.attn == "sdpa" else fast.attn
     marks = {"flash": [], "linear": [], "layernorm": []}
-    real = {"attention": vit_mod.attention, "linear": vit_mod.linear, "layer_norm": vit_mod.layer_norm, "split": vit_mod.layer_norm_split}
+    real = {"attention": vit_mod.attention, "linear": vit_mod.linear, "layer_norm": vit_mod.layer_norm, "split": vit_mod.layer_norm_split,
+            "linear_ln": vit_mod.linear_layer_norm}
     probes_used = [1]
+    try:
+        torch.cuda.Event(enable_timing=True, external=True)
+        ev_kw, inst_mode = {"external": True}, "graph"
+    except TypeError:
+        ev_kw, inst_mode = {}, "eager"
 
-    def bracket(kind, fn, clock=False):
+    def bracket(kind, fn, clock_every=0):
         def wrapped(*a, **kw):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s, e = torch.cuda.Event(enable_timing=True, **ev_kw), torch.cuda.Event(enable_timing=True, **ev_kw)
             s.record()
             o = fn(*a, **kw)
             e.record()
             marks[kind].append((s, e))
-            if clock and probes_used[0] < mhz.numel():
-                probe(probes_used[0])
+            if clock_every and len(marks[kind]) % clock_every == 0 and probes_used[0] < mhz.numel():
+                probe(probes_used[0], 1 << 14)
                 probes_used[0] += 1
             return o
         return wrapped
 
-    inst_steps = max(1, min(args.steps, 5))
+    inst_replays = max(3, min(args.steps, 10))
     fast.graphs = False
-    vit_mod.attention = bracket("flash", real["attention"], clock=True)
-    vit_mod.linear = bracket("linear", real["linear"])
-    vit_mod.layer_norm = bracket("layernorm", real["layer_norm"])
-    vit_mod.layer_norm_split = bracket("layernorm", real["split"])
     runner_env = os.environ.get("FBB_NO_RUNNER")
     os.environ["FBB_NO_RUNNER"] = "1"
+    ei0, ei1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     try:
         step(x_dev)            # untimed: the per-operator path's own first-use costs
-        for v in marks.values():
-            v.clear()
-        probes_used[0] = 1
         torch.cuda.synchronize()
-        ei0, ei1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ei0.record()
-        for _ in range(inst_steps):
-            step(x_dev)
-        ei1.record()
+        vit_mod.attention = bracket("flash", real["attention"], clock_every=4)
+        vit_mod.linear = bracket("linear", real["linear"])
+        vit_mod.linear_layer_norm = bracket("linear", real["linear_ln"])   # a residual GEMM with the LayerNorm after it in its launch
+        vit_mod.layer_norm = bracket("layernorm", real["layer_norm"])
+        vit_mod.layer_norm_split = bracket("layernorm", real["split"])
+        if inst_mode == "graph":
+            ig = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side), torch.cuda.graph(ig, stream=side):
+                step(x_dev)
+            torch.cuda.current_stream().wait_stream(side)
+            for _ in range(inst_replays - 1):
+                ig.replay()
+            ei0.record()
+            ig.replay()            # the events hold the times of this last replay
+            ei1.record()
+            inst_steps = 1
+        else:
+            inst_steps = inst_replays
+            ei0.record()
+            for _ in range(inst_steps):
+                step(x_dev)
+            ei1.record()
         torch.cuda.synchronize()
     finally:
-        vit_mod.attention, vit_mod.linear = real["attention"], real["linear"]
+        vit_mod.attention, vit_mod.linear, vit_mod.linear_layer_norm = real["attention"], real["linear"], real["linear_ln"]
         vit_mod.layer_norm, vit_mod.layer_norm_split = real["layer_norm"], real["split"]
         fast.graphs = graphs
         if runner_env is None:
@@ -325,13 +359,15 @@ def run_ours(args, rank, local_rank, world):
     qkv = torch.randn(1, TOKENS, 3, HEADS, 64, device=dev, dtype=torch.float16)
     q, k, v = qkv.unbind(2)
     o = torch.empty(1, TOKENS, HEADS, 64, device=dev, dtype=torch.float16)
-    for _ in range(3):
-        attention(q, k, v, variant=variant, out=o)
+    alone_ws = Workspaces()   # this graph's own attention scratch memory, made by the warm-up calls below
+    with use_workspaces(alone_ws):
+        for _ in range(3):
+            attention(q, k, v, variant=variant, out=o)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side), torch.cuda.graph(g, stream=side):
+    with torch.cuda.stream(side), torch.cuda.graph(g, stream=side), use_workspaces(alone_ws):
         for _ in range(10):
             attention(q, k, v, variant=variant, out=o)
     torch.cuda.current_stream().wait_stream(side)
@@ -366,6 +402,7 @@ def run_ours(args, rank, local_rank, world):
         kernel_ms = {"flash": per_step["flash"], "linear": per_step["linear"], "layernorm": per_step["layernorm"]}
         # what the eager instrumented step spends outside the three classes: torch's patch-row layout kernels, host gaps
         kernel_ms["other"] = max(0.0, ei0.elapsed_time(ei1) / inst_steps - sum(kernel_ms.values()))
+        kernel_ms["instrumented_step_ms"] = ei0.elapsed_time(ei1) / inst_steps
         line = {
             "metric": "images_per_s", "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "ms_per_image": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -380,11 +417,12 @@ def run_ours(args, rank, local_rank, world):
                     "copy_gbs_needed_per_rank": (h2d + d2h) / (ms_step * 1e-3) / 1e9,
                     "pinned_copy_gbs_per_rank_all_ranks_at_once": {"h2d": [round(b, 1) for b in bw_h2d_ranks], "d2h": [round(b, 1) for b in bw_d2h_ranks]}},
             "gpu_launches": launches_per_step * args.steps,
-            "kernel_ms": {**kernel_ms, "how": f"CUDA events around every launch, eager per-operator pass of {inst_steps} step(s); per step",
+            "kernel_ms": {**kernel_ms, "how": (f"events around every launch of the per-operator path, captured into one graph; the last of {inst_replays} back-to-back replays"
+                                               if inst_mode == "graph" else f"events around every launch, eager per-operator pass of {inst_steps} step(s); per step"),
                           "gap_ms": ms_step - (kernel_ms["flash"] + kernel_ms["linear"] + kernel_ms["layernorm"])},
             "roofline": {"kernel": f"flash64_umma_kernel ({variant})", "bound": "tensor", "achieved": achieved,
                          "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops_burst"],
-                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst (the instrumented pass lasts a fraction of a second)",
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst (a kernel timed on its own; the sustained and nominal fractions are beside it)",
                          "frac_of_measured_sustained": achieved / peaks["tflops_sustained"], "frac_of_nominal_2250": achieved / NOMINAL_FP16_TFLOPS,
                          "launch_ms": attn_mean_ms, "launches_timed": len(attn_ms), "flops_per_launch": FLOPS_ATTN_PER_LAUNCH,
                          "share_of_step": per_step["flash"] / ms_step, "traffic": ATTN_DRAM_TRAFFIC_BYTES,

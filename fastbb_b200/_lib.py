@@ -58,11 +58,15 @@ PROTOTYPES = {
     "fbb_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _f32, _i32, _i32, _vp]),
     "fbb_layernorm_split_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32, _vp]),
     "fbb_linear_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "fbb_linear_layernorm_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _f32, _vp, _i64,
+                                        _vp, _vp]),
+    "fbb_linear_layernorm_launches": (_i32, [_i64, _i32, _i32, _i32]),
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
     "fbb_flash64_f16_ws": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp, _i64, _vp]),
     "fbb_flash64_f16_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_stack_scratch_bytes": (_i64, [_bdp, _i32, _i64]),
+    "fbb_stack_launches": (_i32, [_bdp, _i32, _i64]),
     "fbb_stack_forward_f16": (_i32, [_bdp, _i32, _vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
     "fbb_block_forward_f16": (_i32, [_bdp, _vp, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
 }

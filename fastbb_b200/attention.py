@@ -41,6 +41,17 @@ class Workspaces:
 
     def __init__(self):
         self._by_device = {}
+        self._counters = {}
+
+    def counter(self, device):
+        """A zeroed 4-byte counter on `device` for fbb_linear_layernorm_f16 (every launch leaves it zero again)."""
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        c = self._counters.get(idx)
+        if c is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the counter must exist before a stream capture starts: run the same call once outside the capture first")
+            c = self._counters[idx] = torch.zeros(64, device=device, dtype=torch.int32)
+        return c
 
     def get(self, device, need):
         idx = device.index if device.index is not None else torch.cuda.current_device()
@@ -67,6 +78,23 @@ def use_workspaces(owner):
         yield owner
     finally:
         _ACTIVE.owner = prev
+
+
+_EAGER_OWNERS = collections.OrderedDict()   # (device index, stream handle) -> Workspaces, only for its counter
+
+
+def _counter(device):
+    """Counter for fbb_linear_layernorm_f16 from the active owner, or from a per-(device, stream) table for plain eager calls."""
+    owner = getattr(_ACTIVE, "owner", None)
+    if owner is None:
+        key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(device).cuda_stream)
+        owner = _EAGER_OWNERS.get(key)
+        if owner is None:
+            owner = _EAGER_OWNERS[key] = Workspaces()
+            while len(_EAGER_OWNERS) > _EAGER_MAX:
+                _EAGER_OWNERS.popitem(last=False)
+        _EAGER_OWNERS.move_to_end(key)
+    return owner.counter(device)
 
 
 def _workspace(device, need):

@@ -246,6 +246,30 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
     return launch_linear(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, (cudaStream_t)stream);
 }
 
+int fbb_linear_layernorm_launches(int64_t M, int N, int epilogue, int has_counter) {
+    return linear_layernorm_launches(M, N, epilogue, has_counter != 0);
+}
+
+int fbb_linear_layernorm_f16(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M, int N,
+                             int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate, const void* ln_w,
+                             const void* ln_b, float ln_eps, void* y, int64_t ldy, void* counter, void* stream) {
+    if (A == nullptr || W == nullptr || C == nullptr || y == nullptr) return fail(FBB_ERR_NULL, "linear_layernorm: A, W, C or y is null");
+    if (epilogue != FBB_EPI_NONE && epilogue != FBB_EPI_GELU) return fail(FBB_ERR_ENUM, "linear_layernorm: epilogue must be none or gelu (got %d)", epilogue);
+    if (accumulate != FBB_ACC_F32 && accumulate != FBB_ACC_F16) return fail(FBB_ERR_ENUM, "linear_layernorm: unknown accumulate %d", accumulate);
+    if (M < 0 || M > 0x7FFFFF00ll || N <= 0 || K <= 0) return fail(FBB_ERR_SHAPE, "linear_layernorm: bad M/N/K (%lld, %d, %d)", (long long)M, N, K);
+    if ((K & 7) != 0 || (N & 7) != 0) return fail(FBB_ERR_SHAPE, "linear_layernorm: need K %% 8 == 0 and N %% 8 == 0 (N=%d K=%d)", N, K);
+    if (lda < K || ldw < K || ldc < N || ldy < N || (res != nullptr && ldr < N))
+        return fail(FBB_ERR_SHAPE, "linear_layernorm: a leading dimension is smaller than its row length");
+    if ((lda & 7) || (ldw & 7) || (ldc & 7) || (ldy & 7) || (res != nullptr && (ldr & 7)) || !aligned16(A) || !aligned16(W) || !aligned16(C) ||
+        !aligned16(res) || !aligned16(y) || !aligned16(ln_w) || !aligned16(ln_b))
+        return fail(FBB_ERR_ALIGN, "linear_layernorm: pointers must be 16-byte aligned with leading dimensions %% 8 == 0");
+    if (counter != nullptr && (reinterpret_cast<uintptr_t>(counter) & 3u)) return fail(FBB_ERR_ALIGN, "linear_layernorm: counter must be 4-byte aligned");
+    if (!(ln_eps >= 0.f)) return fail(FBB_ERR_SHAPE, "linear_layernorm: eps must be >= 0");
+    if (y == C) return fail(FBB_ERR_SHAPE, "linear_layernorm: y must not alias C");
+    return launch_linear_layernorm(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, ln_w, ln_b, ln_eps, y, ldy,
+                                   counter, (cudaStream_t)stream);
+}
+
 #endif  // FBB_FLASH_ONLY
 
 int64_t fbb_flash64_workspace_bytes(int B, int N, int H) { return flash64_workspace_bytes_for(B, N, H); }
@@ -301,6 +325,20 @@ int fbb_flash64_f16_static(const void* q, const void* k, const void* v, void* o,
     return launch_flash64(q, k, v, o, B, N, H, qs, ks, vs, os, scale, variant, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+#ifdef FBB_DEBUG_WAITS
+int fbb_debug_waits(unsigned int* out, int max_entries) {
+    unsigned int n = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, g_fbb_debug_n, sizeof(n));
+    if (n > 256u) n = 256u;
+    if ((int)n > max_entries) n = (unsigned)max_entries;
+    cudaMemcpyFromSymbol(out, g_fbb_debug, sizeof(unsigned int) * 5 * n);
+    const unsigned int zero = 0;
+    cudaMemcpyToSymbol(g_fbb_debug_n, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
+
 int fbb_diag_wait_timeout(uint64_t limit_ns, unsigned int detail, void* stream) {
     if (limit_ns == 0 || limit_ns > 100000000ull) return fail(FBB_ERR_SHAPE, "diag: limit must be in (0, 100 ms]");
     wait_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, detail, nullptr);
@@ -318,6 +356,11 @@ int fbb_diag_sm_clock_mhz(float* out_mhz, int64_t spin_clocks, void* stream) {
 int64_t fbb_stack_scratch_bytes(const fbb_block_desc* blocks, int n_blocks, int64_t tokens) {
     if (blocks == nullptr || n_blocks <= 0 || tokens <= 0) return 0;
     return stack_scratch_bytes(blocks, n_blocks, tokens);
+}
+
+int fbb_stack_launches(const fbb_block_desc* blocks, int n_blocks, int64_t tokens) {
+    if (blocks == nullptr || n_blocks <= 0 || tokens <= 0) return 0;
+    return stack_launches(blocks, n_blocks, tokens);
 }
 
 int fbb_stack_forward_f16(const fbb_block_desc* blocks, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes,

@@ -23,6 +23,18 @@ enum DeviceError : unsigned int {
     DEV_TIMEOUT_OTHER = 5,
 };
 
+#ifdef FBB_DEBUG_WAITS
+// Development aid: every wait that gives up or is cut short by the abort flag logs (code, detail, block, warp, parity).
+__device__ unsigned int g_fbb_debug_n = 0;
+__device__ unsigned int g_fbb_debug[256][5];
+__device__ __forceinline__ void debug_log_wait(unsigned int code, unsigned int detail, unsigned int parity) {
+    if ((threadIdx.x & 31) != 0) return;
+    const unsigned int i = atomicAdd(&g_fbb_debug_n, 1u);
+    if (i < 256) {
+        g_fbb_debug[i][0] = code; g_fbb_debug[i][1] = detail; g_fbb_debug[i][2] = blockIdx.x; g_fbb_debug[i][3] = threadIdx.x >> 5; g_fbb_debug[i][4] = parity;
+    }
+}
+#endif
 __device__ __forceinline__ void report_error(unsigned int code, unsigned int detail) {
     if (atomicCAS(&g_fbb_status[0], 0u, code) == 0u) {
         g_fbb_status[1] = detail;
@@ -88,7 +100,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 
 // Wait limit: 2 s of wall time (checked every 256 polls). A healthy pipeline never comes near it.
+#ifdef FBB_DEBUG_WAITS
+constexpr uint64_t kWaitLimitNs = 20000000ull;
+#else
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+#endif
 
 // Returns true when the phase with `parity` completed; false after `limit_ns` (error recorded, *abort set).
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code,
@@ -99,8 +115,15 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
+#ifdef FBB_DEBUG_WAITS
+        if (*abort_flag) { debug_log_wait(code, detail, parity); return false; }
+#else
         if (*abort_flag) return false;
+#endif
         if (globaltimer_ns() - t0 > limit_ns) {
+#ifdef FBB_DEBUG_WAITS
+            debug_log_wait(code + 100u, detail, parity);
+#endif
             report_error(code, detail);
             *abort_flag = 1;
             __threadfence_block();
@@ -332,6 +355,35 @@ __device__ __forceinline__ void umma_commit_pair_warp(uint32_t bar) {
         "}\n"
         ::"r"(bar)
         : "memory");
+}
+
+// The same for a pair inside a larger cluster: `mask` has the bits of the two CTAs' ranks in the cluster.
+__device__ __forceinline__ void umma_commit_pair_mask_warp(uint32_t bar, uint32_t mask) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        ".reg .b16 m;\n\t"
+        "cvt.u16.u32 m, %1;\n\t"
+        "elect.sync _|q, 0xFFFFFFFF;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
+        "}\n"
+        ::"r"(bar), "r"(mask)
+        : "memory");
+}
+// Two floats from the shared memory of CTA `rank` of this cluster, at the offset `addr` has in this CTA (distributed
+// shared memory; the data must have been published by a cluster barrier).
+__device__ __forceinline__ float2 ld_cluster_f32x2(uint32_t addr, uint32_t rank) {
+    float2 v;
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %2, %3;\n\t"
+        "ld.shared::cluster.v2.f32 {%0, %1}, [ra];\n\t"
+        "}\n"
+        : "=f"(v.x), "=f"(v.y)
+        : "r"(addr), "r"(rank)
+        : "memory");
+    return v;
 }
 
 // ---------------------------------------------------------------------------------------------- math

@@ -92,8 +92,8 @@ struct FlashSmem {
     static constexpr int kKOff = 2 * kTileBytes;                     // stages x 16 KB
     static constexpr int kVOff = kKOff + kKVStages * kTileBytes;     // stages x 16 KB
     static constexpr int kBarOff = kVOff + kKVStages * kTileBytes;
-    // barriers: q_full, q_empty, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_done[2], s_free[2]
-    static constexpr int kNumBars = 2 + 4 * kKVStages + 8;
+    // barriers: q_full, q_empty, k_full[S], v_full[S], k_empty[S], v_empty[S], s_full[2], p_ready[2], pv_done[2], s_free[2], t1_go
+    static constexpr int kNumBars = 2 + 4 * kKVStages + 8 + 1;
     static constexpr int kTailOff = kBarOff + kNumBars * 8 + 16;    // TailItems (40 bytes)
     static constexpr int kBytes = kTailOff + 48;
     // No slack for aligning by hand (the array is declared 1024-byte aligned): 160.4 KB keeps the CTA inside the 164 KB
@@ -205,6 +205,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto p_ready = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 2 + t); };
     auto pv_done = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 4 + t); };
     auto s_free = [&](int t) { return bar0 + 8u * (2 + 4 * kKVStages + 6 + t); };
+    const uint32_t t1_go = bar0 + 8u * (2 + 4 * kKVStages + 8);  // completes once: tile 0's issuer has seen its group take the first block
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + S::kBarOff + S::kNumBars * 8);
     volatile int* s_abort = reinterpret_cast<volatile int*>(gen + S::kBarOff + S::kNumBars * 8 + 4);
     TailItems* s_tail = reinterpret_cast<TailItems*>(gen + S::kTailOff);
@@ -228,6 +229,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(pv_done(t), 1);
             mbar_init(s_free(t), 8);
         }
+        mbar_init(t1_go, 1);
         *s_abort = 0;
         // this CTA's share [tb, te) of the tail region's units, cut into items at group boundaries
         long long tb = 0, te = 0;
@@ -352,7 +354,9 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // Tile 1 starts once tile 0's group has its first block in registers: the two groups then run slightly out of
         // step, so that one group's load / maximum / store phases overlap the other group's exponentials (measured at
         // N = 6145: 668 -> 695 TFLOP/s for ff, 600 -> 667 for hh; longer offsets change nothing).
-        if (ok && t == 1 && (n_items > 1 || kb1 - kb > 2)) ok = all_ok(mbar_wait(s_free(0), 0, s_abort, DEV_TIMEOUT_TMEM_EMPTY, 50));
+        // (a barrier of its own that completes exactly once: waiting on s_free(0) by parity could be overtaken by tile 0's
+        // second block and then never return)
+        if (ok && t == 1 && (n_items > 1 || kb1 - kb > 2)) ok = all_ok(mbar_wait(t1_go, 0, s_abort, DEV_TIMEOUT_TMEM_EMPTY, 50));
         if (ok) {
             tc_fence_after();
             issue_qk(0, kb + 1 == kb1);
@@ -378,6 +382,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             if (have_next) {
                 if (!all_ok(mbar_wait(s_free(t), g & 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, t))) { ok = false; break; }
+                if (NQ == 2 && t == 0 && g == 0 && lane == 0) mbar_arrive(t1_go);  // tile 1 may start (see the gate above)
                 if (nfirst && !all_ok(mbar_wait(q_full, (uint32_t)nit & 1u, s_abort, DEV_TIMEOUT_TMA_FULL, 101))) { ok = false; break; }
                 if (!all_ok(mbar_wait(k_full(sn), phn, s_abort, DEV_TIMEOUT_TMA_FULL, sn))) { ok = false; break; }
                 tc_fence_after();
@@ -445,15 +450,18 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tc_fence_after();
                 if (u == 0) FBB_TRACE(t, g, 1);
                 if (!warp_has_rows) {
-                    // S_t(g+1) can be ready long before the other warps have written P_t(g): this warp's arrival for
-                    // unit g must not land in the phase of unit g-1, so it watches that phase complete first.
-                    if (g > 0 && !mbar_wait(p_ready(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_OTHER, 210 + t)) { ok = false; break; }
+                    // This warp only keeps the barriers moving. Its arrival for unit g must wait until the issuer has taken
+                    // p_ready of unit g-1 (it commits pv_done right after issuing that unit's P.V): a tile whose warps are
+                    // all padding would otherwise complete p_ready for g-1 and for g back to back, and the issuer, which
+                    // waits by phase parity, would see the barrier back at the parity it started from and never wake up.
+                    // (Working warps are held the same way by their own wait for pv_done before they overwrite P.)
+                    // S_t is released at once (the next Q K^T needs no more from this warp; its arrival for unit g + 1 can
+                    // only follow S_t(g+1), which the issuer computes after it has seen this unit's release).
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(s_free(t));
-                        mbar_arrive(p_ready(t));
-                    }
+                    if (lane == 0) mbar_arrive(s_free(t));
+                    if (g > 0 && !mbar_wait(pv_done(t), (g - 1u) & 1u, s_abort, DEV_TIMEOUT_OTHER, 210 + t)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive(p_ready(t));
                     continue;
                 }
                 uint32_t r[64];

@@ -51,7 +51,62 @@ struct GemmArgs {
     int act;           // 0 none, 1 gelu
     int acc_f16;       // 1: fp16 accumulator
     int tiles_m, tiles_n;
+    // rows [gemv_row0, gemv_row0 + gemv_rows) have no tile: the epilogue warps compute them (see remainder_rows_by_gemv)
+    const __half* A;
+    const __half* W;
+    int64_t lda, ldw;
+    int gemv_row0, gemv_rows;
 };
+
+// The few rows beyond the last full row tile (every ViT token count is a multiple of the tile height plus the cls token:
+// 257, 4097, 6145, 16385; batched, a handful of rows) do not get a tile of their own, which would cost a whole tile's
+// main loop for one row (M = 6145 with 256-row pair tiles: 300 tiles on 74 pairs = 5 waves, 288 = 4 waves without them).
+// The epilogue warps, idle until the first accumulator completes, compute them as dot products on the CUDA cores: one
+// output element per warp at a time, fp32 accumulation, the same epilogue (bias -> GELU | SwiGLU -> res + gamma * v).
+constexpr int kGemvMaxRows = 8;
+
+__device__ __forceinline__ float warp_dot_f16(const __half* a, const __half* w, int nvec, int lane) {
+    const uint4* ap = reinterpret_cast<const uint4*>(a);
+    const uint4* wp = reinterpret_cast<const uint4*>(w);
+    float acc = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+        const uint4 av = ap[v];  // A was written by the previous kernel: ordinary loads
+        const uint4 wv = __ldg(wp + v);
+        const __half2* ah = reinterpret_cast<const __half2*>(&av);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 af = __half22float2(ah[j]), wf = __half22float2(wh[j]);
+            acc = fmaf(af.x, wf.x, acc);
+            acc = fmaf(af.y, wf.y, acc);
+        }
+    }
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+    return acc;
+}
+
+// warp_global / total_warps: this warp's index among all epilogue warps of the grid. swiglu: W holds [x1 rows | x2 rows].
+__device__ __forceinline__ void remainder_rows_by_gemv(const GemmArgs& g, bool swiglu, int warp_global, int total_warps, int lane) {
+    const int nvec = g.K >> 3;
+    for (int o = warp_global; o < g.gemv_rows * g.n_out; o += total_warps) {
+        const int mi = o / g.n_out, n = o - mi * g.n_out;
+        const int64_t m = g.gemv_row0 + mi;
+        const __half* a = g.A + m * g.lda;
+        float v = warp_dot_f16(a, g.W + (int64_t)n * g.ldw, nvec, lane) + (g.bias != nullptr ? __half2float(g.bias[n]) : 0.f);
+        if (swiglu) {
+            const int n2 = g.N / 2 + n;
+            const float x2 = warp_dot_f16(a, g.W + (int64_t)n2 * g.ldw, nvec, lane) + (g.bias != nullptr ? __half2float(g.bias[n2]) : 0.f);
+            v = silu(v) * x2;
+        } else if (g.act == 1) {
+            v = gelu_erf(v);
+        }
+        if (lane == 0) {
+            if (g.res != nullptr) v = fmaf(g.gamma != nullptr ? __half2float(g.gamma[n]) : 1.f, v, __half2float(g.res[m * g.ldr + n]));
+            g.C[m * g.ldc + n] = __float2half_rn(v);
+        }
+    }
+}
 
 template <int BN, bool SWIGLU, bool CTA2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -200,6 +255,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const int et = threadIdx.x - 64;  // 0..255
         uint8_t* stage_gen = gen + S::kStoreOffset + ew * 2048;
         const uint32_t stage_addr = base + S::kStoreOffset + ew * 2048;
+        if (g.gemv_rows > 0) remainder_rows_by_gemv(g, SWIGLU, (int)blockIdx.x * 8 + ew, (int)gridDim.x * 8, lane);
         int acc = 0;
         uint32_t acc_ph = 0;
         for (int tile = worker; tile < num_tiles; tile += num_workers) {
@@ -337,10 +393,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 // (two waves, the second a third full); as 24 x 3 items of 352 columns it is one wave, and per k-block a CTA stages
 // 16 KB of A and w x 64 bytes of W for w / 256 x 512 tensor clocks (55 bytes per clock at w = 352, against 96 for the
 // one-CTA 256-column tile and 64 for the pair tile).
-// The few rows beyond the last full 256-row tile (every ViT token count is a multiple of the tile height plus the cls
-// token) do not get a tile of their own, which would cost a whole item's time for one row: the epilogue warps, idle
-// during the main loop, compute them as dot products on the CUDA cores (`gemv_rows`, at most kGemvMaxRows).
-constexpr int kGemvMaxRows = 8;
+// The few rows beyond the last full 256-row tile are left to the epilogue warps (remainder_rows_by_gemv), as in the
+// persistent forms.
 constexpr int kWideMaxCols = 512;
 
 struct WideArgs {
@@ -357,10 +411,20 @@ struct WideArgs {
     int chunks;                // items per 256-row tile: ceil(N / w)
     int gemv_row0, gemv_rows;  // rows [gemv_row0, gemv_row0 + gemv_rows) are left to the epilogue warps
     int stages, stage_bytes;   // operand ring: stage = A tile (16 KB) | this CTA's wa/2 rows of W | its wb/2 rows of W
+    // Fused LayerNorm of the output rows (ln_y != null): y[m, :] = LN(C[m, :]) * ln_w + ln_b, fp16. The cluster then holds
+    // all `chunks` items of a 256-row tile (2 * chunks CTAs), which exchange per-row statistics through shared memory.
+    __half* ln_y;
+    const __half* ln_w;
+    const __half* ln_b;
+    float ln_eps;
+    int64_t ldy;
+    unsigned* ln_counter;      // zero between launches: counts finished remainder-row elements (see the GEMV part)
 };
 
 struct WideSmem {
-    static constexpr int kParamBytes = 2 * kWideMaxCols * 4;  // bias + gamma of the item's columns (fp32)
+    // bias + gamma of the item's columns, LayerNorm weight + bias of them (fp32), then per-row statistics: the two
+    // epilogue warp groups' partial (mean, M2), the CTA's partial, and the final (mean, rstd), 128 rows each
+    static constexpr int kParamBytes = 4 * kWideMaxCols * 4 + 4 * 128 * 8;
     static constexpr int kStoreBytes = 8 * 32 * 32 * 2;       // one [32 x 32] fp16 staging tile per epilogue warp
     static constexpr int kMaxStages = 8;
     static constexpr int kNumBars = 2 * kMaxStages + 1;
@@ -375,9 +439,12 @@ struct WideSmem {
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_wa,
-                        const __grid_constant__ CUtensorMap tmap_wb, const __grid_constant__ CUtensorMap tmap_c, const WideArgs g) {
+                        const __grid_constant__ CUtensorMap tmap_wb, const __grid_constant__ CUtensorMap tmap_c,
+                        const __grid_constant__ CUtensorMap tmap_y, const WideArgs g) {
     using S = WideSmem;
-    const uint32_t rank = cluster_ctarank();
+    const uint32_t crank = cluster_ctarank();  // a pair is two CTAs of adjacent ranks; with LayerNorm the cluster holds `chunks` pairs
+    const uint32_t rank = crank & 1u;
+    const bool fuse_ln = g.ln_y != nullptr;
     const int item = (int)(blockIdx.x >> 1);
     const int mt = item / g.chunks;
     const int n0 = (item - mt * g.chunks) * g.w;
@@ -389,6 +456,11 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int ring = g.stages * g.stage_bytes;
     float* s_bias = reinterpret_cast<float*>(gen + ring);
     float* s_gamma = s_bias + kWideMaxCols;
+    float* s_lnw = s_gamma + kWideMaxCols;
+    float* s_lnb = s_lnw + kWideMaxCols;
+    float2* s_part_wg = reinterpret_cast<float2*>(s_lnb + kWideMaxCols);  // [2][128]: (mean, M2) of each warp group's columns
+    float2* s_part_cta = s_part_wg + 256;                                 // [128]: (mean, M2) of this CTA's columns
+    float2* s_row_stat = s_part_cta + 128;                                // [128]: (mean, rstd) of the whole row
     const int store_off = ring + S::kParamBytes;
     const uint32_t bar0 = base + store_off + S::kStoreBytes;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -413,6 +485,7 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         tma_prefetch_desc(&tmap_wa);
         tma_prefetch_desc(&tmap_wb);
         tma_prefetch_desc(&tmap_c);
+        if (fuse_ln) tma_prefetch_desc(&tmap_y);
     }
     if (warp == 1) {
         __syncwarp();
@@ -469,44 +542,85 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 umma_ss_pair_warp(d_a, adesc + 2u * k, bdesc_a + 2u * k, idesc_a, accumulate);
                 if (g.wb > 0) umma_ss_pair_warp(d_b, adesc + 2u * k, bdesc_b + 2u * k, idesc_b, accumulate);
             }
-            umma_commit_pair_warp(empty_bar(s));  // frees the stage in both CTAs
+            umma_commit_pair_mask_warp(empty_bar(s), 3u << crank);  // frees the stage in both CTAs (the leader's rank is even)
             if (++s == g.stages) { s = 0; ph ^= 1u; }
         }
-        if (ok) umma_commit_pair_warp(tfull_bar);  // both CTAs' accumulators complete
+        if (ok) umma_commit_pair_mask_warp(tfull_bar, 3u << crank);  // both CTAs' accumulators complete
     } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue warps
         const int ew = warp - 2;
         const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
         const int et = threadIdx.x - 64;
-        // (1) while the main loop runs: the rows that have no tile, one output element per warp at a time
+        // (1) while the main loop runs: the rows that have no tile (remainder_rows_by_gemv)
         if (g.gemv_rows > 0) {
-            const int total_warps = (int)gridDim.x * 8;
-            const int nvec = g.K >> 3;
-            for (int o = (int)blockIdx.x * 8 + ew; o < g.gemv_rows * g.N; o += total_warps) {
-                const int mi = o / g.N, n = o - mi * g.N;
-                const int64_t m = g.gemv_row0 + mi;
-                const uint4* ap = reinterpret_cast<const uint4*>(g.A + m * g.lda);
-                const uint4* wp = reinterpret_cast<const uint4*>(g.W + (int64_t)n * g.ldw);
-                float acc = 0.f;
-                for (int v = lane; v < nvec; v += 32) {
-                    const uint4 av = ap[v];
-                    const uint4 wv = __ldg(wp + v);
-                    const __half2* ah = reinterpret_cast<const __half2*>(&av);
-                    const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 af = __half22float2(ah[j]), wf = __half22float2(wh[j]);
-                        acc = fmaf(af.x, wf.x, acc);
-                        acc = fmaf(af.y, wf.y, acc);
-                    }
-                }
-#pragma unroll
-                for (int sft = 16; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+            GemmArgs r;
+            r.C = g.C; r.bias = g.bias; r.res = g.res; r.gamma = g.gamma;
+            r.M = g.M; r.N = g.N; r.K = g.K; r.n_out = g.N;
+            r.ldc = g.ldc; r.ldr = g.ldr; r.act = g.act; r.acc_f16 = g.acc_f16; r.tiles_m = r.tiles_n = 0;
+            r.A = g.A; r.W = g.W; r.lda = g.lda; r.ldw = g.ldw; r.gemv_row0 = g.gemv_row0; r.gemv_rows = g.gemv_rows;
+            const int gw = (int)blockIdx.x * 8 + ew, total_warps = (int)gridDim.x * 8, total = g.gemv_rows * g.N;
+            remainder_rows_by_gemv(r, false, gw, total_warps, lane);
+            if (fuse_ln && gw < total) {
+                // LayerNorm of those rows: their elements are spread over the warps of the whole grid, so each warp adds the
+                // number it has written to a counter, and the warp whose addition completes the count normalises the rows
+                // (nobody waits for anybody). It leaves the counter at zero for the next launch on the stream.
+                const int mine = (total - gw + total_warps - 1) / total_warps;
+                int last = 0;
                 if (lane == 0) {
-                    float v = acc + (g.bias != nullptr ? __half2float(g.bias[n]) : 0.f);
-                    if (g.act == 1) v = gelu_erf(v);
-                    if (g.res != nullptr) v = fmaf(g.gamma != nullptr ? __half2float(g.gamma[n]) : 1.f, v, __half2float(g.res[m * g.ldr + n]));
-                    g.C[m * g.ldc + n] = __float2half_rn(v);
+                    __threadfence();
+                    last = atomicAdd(g.ln_counter, (unsigned)mine) + (unsigned)mine == (unsigned)total;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int nvec = g.N >> 3;
+                    for (int mi = 0; mi < g.gemv_rows; ++mi) {
+                        const int64_t m = g.gemv_row0 + mi;
+                        const uint4* xr = reinterpret_cast<const uint4*>(g.C + m * g.ldc);
+                        float sum = 0.f;
+                        for (int v = lane; v < nvec; v += 32) {
+                            const uint4 xv = __ldcg(xr + v);
+                            const __half2* h = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __half22float2(h[j]);
+                                sum += f.x + f.y;
+                            }
+                        }
+#pragma unroll
+                        for (int sft = 16; sft > 0; sft >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sft);
+                        const float mean = sum / (float)g.N;
+                        float q = 0.f;
+                        for (int v = lane; v < nvec; v += 32) {
+                            const uint4 xv = __ldcg(xr + v);
+                            const __half2* h = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __half22float2(h[j]);
+                                q += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+                            }
+                        }
+#pragma unroll
+                        for (int sft = 16; sft > 0; sft >>= 1) q += __shfl_xor_sync(0xffffffffu, q, sft);
+                        const float rstd = rsqrtf(q / (float)g.N + g.ln_eps);
+                        uint4* yr = reinterpret_cast<uint4*>(g.ln_y + m * g.ldy);
+                        for (int v = lane; v < nvec; v += 32) {
+                            const uint4 xv = __ldcg(xr + v);
+                            const __half2* h = reinterpret_cast<const __half2*>(&xv);
+                            uint4 out;
+                            uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __half22float2(h[j]);
+                                const int c = v * 8 + 2 * j;
+                                const float w0 = g.ln_w != nullptr ? __half2float(g.ln_w[c]) : 1.f, w1 = g.ln_w != nullptr ? __half2float(g.ln_w[c + 1]) : 1.f;
+                                const float b0 = g.ln_b != nullptr ? __half2float(g.ln_b[c]) : 0.f, b1 = g.ln_b != nullptr ? __half2float(g.ln_b[c + 1]) : 0.f;
+                                o[j] = pack_h2(fmaf((f.x - mean) * rstd, w0, b0), fmaf((f.y - mean) * rstd, w1, b1));
+                            }
+                            yr[v] = out;
+                        }
+                    }
+                    if (lane == 0) *g.ln_counter = 0u;
                 }
             }
         }
@@ -516,6 +630,10 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const bool in = col < g.N;
             s_bias[i] = (g.bias != nullptr && in) ? __half2float(g.bias[col]) : 0.f;
             s_gamma[i] = (g.gamma != nullptr && in) ? __half2float(g.gamma[col]) : 1.f;
+            if (fuse_ln) {
+                s_lnw[i] = (g.ln_w != nullptr && in) ? __half2float(g.ln_w[col]) : 1.f;
+                s_lnb[i] = (g.ln_b != nullptr && in) ? __half2float(g.ln_b[col]) : 0.f;
+            }
         }
         named_bar_sync(1, kEpiThreads);
         // (3) the accumulators: 32-column chunks, even chunks to warps 0-3, odd chunks to warps 4-7
@@ -538,6 +656,12 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         };
 #pragma unroll
         for (int ci = 0; ci < kResRing; ++ci) load_res(ci, rr[ci]);
+        // With LayerNorm: running (count, mean, M2) of the fp16-rounded output values of this thread's row over its chunks
+        // (Chan's merge of per-chunk two-pass statistics: no E[x^2] - E[x]^2 cancellation), and the rounded values
+        // themselves parked in the operand ring, which is free once the accumulators are complete.
+        float ln_cnt = 0.f, ln_mean = 0.f, ln_m2 = 0.f;
+        const int stash_stride = g.w * 2 + 16;  // bytes; (stride / 16) is odd: conflict-free 16-byte accesses down a column
+        uint8_t* stash_row = gen + (quad * 32 + lane) * stash_stride;
         if (mbar_wait(tfull_bar, 0u, s_abort, DEV_TIMEOUT_TMEM_FULL, 0)) {
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -577,14 +701,14 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 }
                 if (lane == 0) bulk_wait_read_all();
                 __syncwarp();
+                uint4 ov[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    uint4 o;
-                    o.x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
-                    o.y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
-                    o.z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
-                    o.w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
-                    *reinterpret_cast<uint4*>(stage_gen + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+                    ov[q].x = pack_h2(v[q * 8 + 0], v[q * 8 + 1]);
+                    ov[q].y = pack_h2(v[q * 8 + 2], v[q * 8 + 3]);
+                    ov[q].z = pack_h2(v[q * 8 + 4], v[q * 8 + 5]);
+                    ov[q].w = pack_h2(v[q * 8 + 6], v[q * 8 + 7]);
+                    *reinterpret_cast<uint4*>(stage_gen + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = ov[q];
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -592,14 +716,112 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     tma_store_2d(&tmap_c, stage_addr, n0 + c0, m0 + quad * 32);
                     bulk_commit();
                 }
+                if (fuse_ln) {
+                    float csum = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        *reinterpret_cast<uint4*>(stash_row + c0 * 2 + q * 16) = ov[q];
+                        const __half2* h = reinterpret_cast<const __half2*>(&ov[q]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __half22float2(h[j]);
+                            v[q * 8 + 2 * j] = f.x;
+                            v[q * 8 + 2 * j + 1] = f.y;
+                            csum += f.x + f.y;
+                        }
+                    }
+                    const float cmean = csum * (1.f / 32.f);
+                    float cm2 = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) cm2 = fmaf(v[j] - cmean, v[j] - cmean, cm2);
+                    const float d = cmean - ln_mean, tot = ln_cnt + 32.f;
+                    ln_mean += d * (32.f / tot);
+                    ln_m2 += cm2 + d * d * (ln_cnt * 32.f / tot);
+                    ln_cnt = tot;
+                }
+            }
+        }
+        if (fuse_ln) {
+            // the two warp groups hold the even / odd chunks of the same rows: merge them into the CTA's partial per row
+            const int rloc = quad * 32 + lane;
+            s_part_wg[(ew >> 2) * 128 + rloc] = make_float2(ln_mean, ln_m2);
+            named_bar_sync(1, kEpiThreads);
+            if ((ew >> 2) == 0) {
+                const int cols = min(g.w, g.N - n0);                    // valid columns of this item (multiples of 32)
+                const float cnt1 = (float)(32 * (cols / 64)), cnt0 = (float)cols - cnt1;  // odd chunks / even chunks
+                const float2 p1 = s_part_wg[128 + rloc];
+                float mean = ln_mean, m2 = ln_m2;
+                if (cnt1 > 0.f) {
+                    const float d = p1.x - mean, tot = cnt0 + cnt1;
+                    mean += d * (cnt1 / tot);
+                    m2 += p1.y + d * d * (cnt0 * cnt1 / tot);
+                }
+                s_part_cta[rloc] = make_float2(mean, m2);
             }
         }
         if (lane == 0) bulk_wait_all();
     }
 
+    if (fuse_ln) {
+        // Every CTA of the cluster has its per-row partials in shared memory; the CTAs that hold the other column ranges of
+        // the same rows (same parity of rank) are read through distributed shared memory. All threads take the barrier.
+        __syncthreads();
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int ew = warp - 2, quad = warp & 3, rloc = quad * 32 + lane;
+            if ((ew >> 2) == 0) {
+                const int my_chunk = (int)(crank >> 1);
+                const float2 mine = s_part_cta[rloc];
+                float cnt = (float)min(g.w, g.N - n0), mean = mine.x, m2 = mine.y;
+                for (int k = 0; k < g.chunks; ++k) {
+                    if (k == my_chunk) continue;
+                    const float2 p = ld_cluster_f32x2(smem_u32(&s_part_cta[rloc]), (uint32_t)(2 * k) | rank);
+                    const float cntk = (float)min(g.w, g.N - k * g.w);
+                    const float d = p.x - mean, tot = cnt + cntk;
+                    mean += d * (cntk / tot);
+                    m2 += p.y + d * d * (cnt * cntk / tot);
+                    cnt = tot;
+                }
+                s_row_stat[rloc] = make_float2(mean, rsqrtf(m2 / cnt + g.ln_eps));
+            }
+            named_bar_sync(1, kEpiThreads);
+            // second pass: the parked fp16 values, normalised, out through the staging tile to y
+            const float2 st = s_row_stat[rloc];
+            uint8_t* stage_gen = gen + store_off + ew * 2048;
+            const uint32_t stage_addr = base + store_off + ew * 2048;
+            const uint8_t* stash_row = gen + rloc * (g.w * 2 + 16);
+#pragma unroll 1
+            for (int c0 = (ew >> 2) * 32; c0 < g.w && n0 + c0 < g.N; c0 += 64) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(stash_row + c0 * 2 + q * 16);
+                    const __half2* h = reinterpret_cast<const __half2*>(&xv);
+                    uint4 o;
+                    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(h[j]);
+                        const int c = c0 + q * 8 + 2 * j;
+                        op[j] = pack_h2(fmaf((f.x - st.x) * st.y, s_lnw[c], s_lnb[c]), fmaf((f.y - st.x) * st.y, s_lnw[c + 1], s_lnb[c + 1]));
+                    }
+                    *reinterpret_cast<uint4*>(stage_gen + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && m0 + quad * 32 < g.M) {
+                    tma_store_2d(&tmap_y, stage_addr, n0 + c0, m0 + quad * 32);
+                    bulk_commit();
+                }
+            }
+            if (lane == 0) bulk_wait_all();
+        }
+    }
+
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();  // the peer may still be signalling this CTA's barriers / reading its operands
+    cluster_sync_all();  // the peers may still be signalling this CTA's barriers / reading its operands or statistics
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
@@ -638,6 +860,13 @@ static int max_pairs() {
     return cached[dev] > 0 ? cached[dev] : 0;
 }
 
+// Rows left to the epilogue warps when M is a few rows more than a multiple of the tile height, and the row tiles then.
+static int remainder_rows(int64_t M, int tile_rows) {
+    const int r = (int)(M % tile_rows);
+    return (M >= tile_rows && r > 0 && r <= kGemvMaxRows) ? r : 0;
+}
+static int64_t row_tiles(int64_t M, int tile_rows) { return remainder_rows(M, tile_rows) > 0 ? M / tile_rows : (M + tile_rows - 1) / tile_rows; }
+
 template <int BN, bool SWIGLU, bool CTA2>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmArgs g, cudaStream_t stream) {
     using S = GemmSmem<BN, CTA2>;
@@ -652,7 +881,9 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     }
     constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
     constexpr int kTileRows = CTA2 ? 2 * BM : BM;
-    g.tiles_m = (g.M + kTileRows - 1) / kTileRows;
+    g.gemv_rows = remainder_rows(g.M, kTileRows);
+    g.tiles_m = (int)row_tiles(g.M, kTileRows);
+    g.gemv_row0 = g.gemv_rows > 0 ? g.tiles_m * kTileRows : g.M;
     g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
     const int tiles = g.tiles_m * g.tiles_n;
     const int workers_max = CTA2 ? max_pairs<BN, SWIGLU>() : num_sms();
@@ -663,22 +894,25 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     return FBB_OK;
 }
 
-// Pairs of the wide kernel that can be resident at once on the current device (0: cannot be launched).
-static int wide_max_pairs() {
-    static int cached[64] = {};
+// Clusters of `cluster_ctas` CTAs (2: a pair; 4, 6, 8: the pairs of a row tile that exchange LayerNorm statistics) of the
+// wide kernel that can be resident at once on the current device (0: cannot be launched).
+static int wide_max_clusters(int cluster_ctas) {
+    static int cached[64][5] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return 0;
-    if (cached[dev] == 0) {
+    const int slot = cluster_ctas / 2;
+    if (dev < 0 || dev >= 64 || slot < 1 || slot > 4) return 0;
+    if (cached[dev][slot] == 0) {
         int n = 0;
-        if (cudaFuncSetAttribute(linear_wide_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kMaxDynamic) == cudaSuccess) {
+        bool ok = cudaFuncSetAttribute(linear_wide_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kMaxDynamic) == cudaSuccess;
+        if (ok) {
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(2 * num_sms());
+            cfg.gridDim = dim3((unsigned)(cluster_ctas * num_sms()));
             cfg.blockDim = dim3(kGemmThreads);
             cfg.dynamicSmemBytes = WideSmem::kMaxDynamic;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.x = (unsigned)cluster_ctas;
             attr[0].val.clusterDim.y = 1;
             attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr;
@@ -686,21 +920,36 @@ static int wide_max_pairs() {
             if (cudaOccupancyMaxActiveClusters(&n, linear_wide_pair_kernel, &cfg) != cudaSuccess) n = 0;
             cudaGetLastError();
         }
-        cached[dev] = n > 0 ? n : -1;
+        cached[dev][slot] = n > 0 ? n : -1;
     }
-    return cached[dev] > 0 ? cached[dev] : 0;
+    return cached[dev][slot] > 0 ? cached[dev][slot] : 0;
 }
+static int wide_max_pairs() { return wide_max_clusters(2); }
 
 // Rows the wide form leaves to its epilogue warps: the remainder beyond the last full 256-row tile when it is small.
-static int wide_gemv_rows(int64_t M) {
-    const int r = (int)(M % (2 * BM));
-    return (M >= 2 * BM && r > 0 && r <= kGemvMaxRows) ? r : 0;
-}
-static int64_t wide_row_tiles(int64_t M) { return wide_gemv_rows(M) > 0 ? M / (2 * BM) : (M + 2 * BM - 1) / (2 * BM); }
+static int wide_gemv_rows(int64_t M) { return remainder_rows(M, 2 * BM); }
+static int64_t wide_row_tiles(int64_t M) { return row_tiles(M, 2 * BM); }
 
-static int launch_wide(const void* A, const void* W, void* C, const GemmArgs& base, int64_t lda, int64_t ldw, int w, cudaStream_t stream) {
+// LayerNorm fused into the launch (see WideArgs); y == null: none.
+struct WideLn {
+    void* y = nullptr;
+    const void* w = nullptr;
+    const void* b = nullptr;
+    float eps = 0.f;
+    int64_t ldy = 0;
+    unsigned* counter = nullptr;
+};
+
+static int launch_wide(const void* A, const void* W, void* C, const GemmArgs& base, int64_t lda, int64_t ldw, int w, cudaStream_t stream,
+                       const WideLn& ln = WideLn()) {
     if (wide_max_pairs() == 0) return fail(FBB_ERR_SHAPE, "linear: this device cannot co-schedule CTA pairs");
     WideArgs g;
+    g.ln_y = reinterpret_cast<__half*>(ln.y);
+    g.ln_w = reinterpret_cast<const __half*>(ln.w);
+    g.ln_b = reinterpret_cast<const __half*>(ln.b);
+    g.ln_eps = ln.eps;
+    g.ldy = ln.ldy;
+    g.ln_counter = ln.counter;
     g.A = reinterpret_cast<const __half*>(A);
     g.W = reinterpret_cast<const __half*>(W);
     g.C = base.C;
@@ -746,11 +995,91 @@ static int launch_wide(const void* A, const void* W, void* C, const GemmArgs& ba
     uint32_t box_c[2] = {32, 32};
     st = make_tmap_f16(&tc, C, 2, dims_c, str_c, box_c, CU_TENSOR_MAP_SWIZZLE_64B);
     if (st != FBB_OK) return st;
+    CUtensorMap ty = tc;
+    if (ln.y != nullptr) {
+        int64_t str_y[2] = {1, ln.ldy};
+        st = make_tmap_f16(&ty, ln.y, 2, dims_c, str_y, box_c, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (st != FBB_OK) return st;
+    }
 
+    const unsigned cluster = ln.y != nullptr ? 2u * (unsigned)g.chunks : 2u;
     cudaError_t e = launch_pdl_cluster(linear_wide_pair_kernel, dim3((unsigned)(2 * items)), dim3(kGemmThreads),
-                                       (size_t)WideSmem::dynamic_bytes(g.stages, g.stage_bytes), stream, 2u, ta, twa, twb, tc, g);
+                                       (size_t)WideSmem::dynamic_bytes(g.stages, g.stage_bytes), stream, cluster, ta, twa, twb, tc, ty, g);
     if (e != cudaSuccess) return fail((int)e, "linear_wide_pair_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
+}
+
+static bool gemm_pairs_enabled();
+
+// Item width of the fused GEMM + LayerNorm launch for this shape, 0 when it runs as two launches: the most column chunks
+// (narrowest items, at most four pairs = eight CTAs per cluster) for which every row tile's cluster is resident at once.
+// The fused form is OFF unless FBB_LN_FUSION=1: measured on B200 it is slower than the GEMM followed by the LayerNorm
+// kernel on every shape of the ViT configurations (us, fused / two launches): M = 6145, N = 1024: K = 1024 33.5 / 23.3,
+// K = 4096 71.8 / 48.7; M = 4097, N = 768: 19.4 / 14.0 and 26.2 / 21.2; M = 5480, N = 1536: 37.7 / 31.2 and 75.5 / 59.2;
+// ViT-L/14 at 6145 tokens 10.4 instead of 9.3 ms per image. Its second epilogue pass and the cluster exchange overlap
+// nothing, clusters of six or eight CTAs place worse than pairs, and the separate LayerNorm (5.4 us, most of it hidden
+// behind its neighbours by programmatic dependent launch) was never the 0.3 ms it looks like in isolation.
+static int fused_layernorm_width(int64_t M, int N, int epilogue, bool has_counter) {
+    const char* on = getenv("FBB_LN_FUSION");
+    if (on == nullptr || on[0] != '1') return 0;
+    if (M <= 0 || epilogue == FBB_EPI_SWIGLU || (N % 32) != 0 || N > 4 * kWideMaxCols || !gemm_pairs_enabled() ||
+        getenv("FBB_GEMM_FORCE") != nullptr || wide_max_pairs() == 0 || (wide_gemv_rows(M) > 0 && !has_counter))
+        return 0;
+    const int64_t tmw = wide_row_tiles(M);
+    for (int chunks = 4; chunks >= 1; --chunks) {
+        const int w = ((N + chunks - 1) / chunks + 31) / 32 * 32;
+        if (w > kWideMaxCols || w < 64 || (N + w - 1) / w != chunks) continue;
+        if (wide_max_clusters(2 * chunks) < tmw) continue;
+        return w;
+    }
+    return 0;
+}
+int linear_layernorm_launches(int64_t M, int N, int epilogue, bool has_counter) {
+    return M <= 0 ? 0 : (fused_layernorm_width(M, N, epilogue, has_counter) > 0 ? 1 : 2);
+}
+
+// out = epilogue(A . W^T) as launch_linear, and y = LayerNorm(out) * ln_w + ln_b. One launch (the wide pair form with the
+// pairs of a row tile in one cluster) when the shape allows it, otherwise the GEMM followed by the LayerNorm kernel.
+int launch_linear_layernorm(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M, int N,
+                            int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate, const void* ln_w,
+                            const void* ln_b, float ln_eps, void* y, int64_t ldy, void* counter, cudaStream_t stream) {
+    if (M == 0) return FBB_OK;
+    {
+        const int w = fused_layernorm_width(M, N, epilogue, counter != nullptr);
+        if (w > 0) {
+            GemmArgs g;
+            g.C = reinterpret_cast<__half*>(C);
+            g.bias = reinterpret_cast<const __half*>(bias);
+            g.res = reinterpret_cast<const __half*>(res);
+            g.gamma = res != nullptr ? reinterpret_cast<const __half*>(gamma) : nullptr;
+            g.M = (int)M;
+            g.N = N;
+            g.K = K;
+            g.n_out = N;
+            g.ldc = ldc;
+            g.ldr = ldr;
+            g.act = epilogue == FBB_EPI_GELU ? 1 : 0;
+            g.acc_f16 = accumulate == FBB_ACC_F16 ? 1 : 0;
+            g.tiles_m = g.tiles_n = 0;
+            g.A = reinterpret_cast<const __half*>(A);
+            g.W = reinterpret_cast<const __half*>(W);
+            g.lda = lda;
+            g.ldw = ldw;
+            g.gemv_row0 = (int)M;
+            g.gemv_rows = 0;
+            WideLn ln;
+            ln.y = y;
+            ln.w = ln_w;
+            ln.b = ln_b;
+            ln.eps = ln_eps;
+            ln.ldy = ldy;
+            ln.counter = reinterpret_cast<unsigned*>(counter);
+            return launch_wide(A, W, C, g, lda, ldw, w, stream, ln);
+        }
+    }
+    const int rc = launch_linear(A, W, C, bias, res, gamma, M, N, K, lda, ldw, ldc, ldr, epilogue, accumulate, stream);
+    if (rc != FBB_OK) return rc;
+    return launch_layernorm(C, y, ln_w, ln_b, M, N, ldc, ldy, ln_eps, FBB_DTYPE_F16, FBB_DTYPE_F16, stream);
 }
 
 static bool gemm_pairs_enabled() {
@@ -782,6 +1111,12 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     g.act = epilogue == FBB_EPI_GELU ? 1 : 0;
     g.acc_f16 = accumulate == FBB_ACC_F16 ? 1 : 0;
     g.tiles_m = g.tiles_n = 0;
+    g.A = reinterpret_cast<const __half*>(A);
+    g.W = reinterpret_cast<const __half*>(W);
+    g.lda = lda;
+    g.ldw = ldw;
+    g.gemv_row0 = (int)M;
+    g.gemv_rows = 0;
 
     // Shape of the work item: one CTA with a 128x256 or 128x128 tile, or a CTA pair with a 256x256 tile (each CTA stages
     // its 128 rows of A and half of the W rows, which cuts the operand traffic from L2 per FLOP by a third).
@@ -795,7 +1130,7 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     const bool pairs_ok = gemm_pairs_enabled();
     const int pairs256 = pairs_ok ? (swiglu ? max_pairs<256, true>() : max_pairs<256, false>()) : 0;
     auto waves = [](int64_t tiles, int workers) { return (double)((tiles + workers - 1) / workers); };
-    const int64_t tm1 = (M + BM - 1) / BM, tm2 = (M + 2 * BM - 1) / (2 * BM);
+    const int64_t tm1 = row_tiles(M, BM), tm2 = row_tiles(M, 2 * BM);  // a remainder of a few rows gets no tile (remainder_rows_by_gemv)
     const int64_t tn256 = (g.n_out + 255) / 256, tn128 = (g.n_out + 127) / 128;
     double best = waves(tm1 * tn256, sms) * 1.0;
     bool use_pairs = false, use128 = false;

@@ -73,6 +73,14 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
                   int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
                   cudaStream_t stream);
 
+// The same followed by y = LayerNorm(C) * ln_w + ln_b (rows of N elements), fused into the GEMM launch when the shape
+// allows. `counter`: 4 bytes of zeroed device memory that every launch leaves zero (needed when M has remainder rows).
+int launch_linear_layernorm(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M, int N,
+                            int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate, const void* ln_w,
+                            const void* ln_b, float ln_eps, void* y, int64_t ldy, void* counter, cudaStream_t stream);
+
+int linear_layernorm_launches(int64_t M, int N, int epilogue, bool has_counter);  // 1: one fused launch, 2: GEMM then LayerNorm
+
 // How many CTA pairs (clusters of two) of the linear kernel with `bn`-column tiles fit on the current device at once.
 int linear_max_pairs(int bn);
 
@@ -87,6 +95,7 @@ int64_t flash64_workspace_bytes_for(int B, int N, int H);
 
 // One FFI crossing per block / stack (block.cu): scratch needed for `tokens` tokens, and the launches themselves.
 int64_t stack_scratch_bytes(const fbb_block_desc* d, int n_blocks, int64_t tokens);
+int stack_launches(const fbb_block_desc* d, int n_blocks, int64_t tokens);  // kernels stack_forward enqueues for this run
 int stack_forward(const fbb_block_desc* d, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes, void* ws,
                   int64_t ws_bytes, cudaStream_t stream);
 

@@ -66,3 +66,45 @@ def linear(x, w, b=None, act=None, res=None, gamma=None, variant="c2", out=None,
             _ACT[act], _ACC[variant], _lib.stream_ptr(x.device)))
     _lib.launched()
     return out
+
+
+def linear_layer_norm(x, w, b=None, act=None, res=None, gamma=None, variant="c2", ln_weight=None, ln_bias=None, eps=1e-6, out=None):
+    """(out, y): out = linear(x, w, b, act, res, gamma) as above (act None or "gelu") and y = LayerNorm(out) * ln_weight +
+    ln_bias over the last dimension, through fbb_linear_layernorm_f16: ONE launch when the shape allows (what a
+    transformer block's proj + norm2, and fc2 + the next block's norm1, become), otherwise the two kernels one after
+    the other. x must be 2-D or 3-D contiguous; out may be `res` itself (in place on the residual stream)."""
+    from .attention import _counter
+    if act not in (None, "none", "gelu"):
+        raise ValueError(f"unsupported activation for the fused form: {act}")
+    if variant not in _ACC:
+        raise ValueError(f"unsupported variant: {variant}")
+    if not (x.is_cuda and x.dtype == torch.float16 and w.dtype == torch.float16 and x.is_contiguous() and w.is_contiguous()):
+        raise ValueError("linear_layer_norm needs contiguous CUDA fp16 x and w (there is no CPU path)")
+    K, N = x.shape[-1], w.shape[0]
+    if w.dim() != 2 or w.shape[1] != K or w.device != x.device:
+        raise ValueError("w must be [N, K] on the input's device")
+    oshape = (*x.shape[:-1], N)
+    for t in (b, gamma, ln_weight, ln_bias):
+        if t is not None and (t.device != x.device or t.dtype != torch.float16 or not t.is_contiguous() or t.numel() != N):
+            raise ValueError("bias / gamma / LayerNorm parameters must be contiguous fp16 vectors of the output width on the input's device")
+    if res is not None and (res.device != x.device or res.dtype != torch.float16 or res.shape != oshape or not res.is_contiguous()):
+        raise ValueError("res must be contiguous fp16 with the output shape on the input's device")
+    if gamma is not None and res is None:
+        raise ValueError("gamma is the LayerScale of the residual epilogue: it needs res")
+    if out is None:
+        out = torch.empty(oshape, device=x.device, dtype=torch.float16)
+    elif out.shape != oshape or out.device != x.device or out.dtype != torch.float16 or not out.is_contiguous():
+        raise ValueError("out must be contiguous fp16 with the output shape on the input's device")
+    y = torch.empty(oshape, device=x.device, dtype=torch.float16)
+    M = x.numel() // K if K else 0
+    if M == 0:
+        return out, y
+    with _on(x.device):
+        lib = _lib.load()
+        counter = _counter(x.device)
+        _lib.check(lib.fbb_linear_layernorm_f16(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(b), _lib.ptr(res), _lib.ptr(gamma), M, N, K, K, K, N, N if res is not None else 0,
+            _ACT[act], _ACC[variant], _lib.ptr(ln_weight), _lib.ptr(ln_bias), float(eps), y.data_ptr(), N, counter.data_ptr(),
+            _lib.stream_ptr(x.device)))
+        _lib.launched(lib.fbb_linear_layernorm_launches(M, N, _ACT[act], 1))
+    return out, y

@@ -23,7 +23,7 @@ import torch.nn.functional as F
 
 from . import _lib
 from .attention import Workspaces, _workspace, attention, use_workspaces
-from .gemm import linear
+from .gemm import linear, linear_layer_norm
 from .layernorm import layer_norm, layer_norm_split
 
 HEAD_DIM = 64
@@ -80,6 +80,51 @@ def run_block(block, x, attn_variant, gacc):
         return linear(h, m.fc2.weight, m.fc2.bias, res=x, gamma=g2, variant=v_fc2)
     h = linear(y, m.w12.weight, m.w12.bias, act="swiglu", variant=v_main)  # DINOv2 SwiGLU FFN (ViT-g)
     return linear(h, m.w3.weight, m.w3.bias, res=x, gamma=g2, variant=v_fc2)
+
+
+def _plain_ln(mod, C):
+    """A LayerNorm over the last dimension with fp16 (or absent) contiguous parameters: what the fused kernels can apply."""
+    return (isinstance(mod, torch.nn.LayerNorm) and tuple(mod.normalized_shape) == (C,)
+            and all(p is None or (p.is_cuda and p.dtype == torch.float16 and p.is_contiguous()) for p in (mod.weight, mod.bias)))
+
+
+def run_blocks_chained(blocks, x, attn_variant, gacc):
+    """The per-operator path over a run of blocks with the same launches as the C stack runner: each residual GEMM carries
+    the LayerNorm that follows it (proj + norm2; fc2 + the next block's norm1) through linear_layer_norm, which is one
+    launch where the shape allows. Same results, bit for bit, as run_stack. x [B, N, C] fp16 contiguous CUDA; returns the
+    new x (the input is not modified). Blocks the fused call does not cover go through run_block."""
+    y = None  # LayerNorm-1 output of the next block, when the previous fc2 launch already produced it
+    for i, block in enumerate(blocks):
+        a, m = block.attn, block.mlp
+        B, N, C = x.shape
+        nxt = blocks[i + 1] if i + 1 < len(blocks) else None
+        fusable = (hasattr(m, "fc1") or hasattr(m, "w12")) and C == a.num_heads * HEAD_DIM and _plain_ln(block.norm2, C)
+        if not fusable:
+            x, y = run_block(block, x, attn_variant, gacc), None
+            continue
+        v_main, v_fc2 = _gemm_variants(gacc)
+        H = a.num_heads
+        y1 = y if y is not None else _norm(block.norm1, x)
+        qkv = linear(y1, a.qkv.weight, a.qkv.bias, variant=v_main).view(B, N, 3, H, HEAD_DIM)
+        q, k, v = qkv.unbind(2)
+        o = attention(q, k, v, scale=getattr(a, "scale", None), variant="ff" if attn_variant == "sdpa" else attn_variant)
+        n2 = block.norm2
+        x, y2 = linear_layer_norm(o.view(B, N, C), a.proj.weight, a.proj.bias, res=x, gamma=_gamma(block, "ls1"), variant=v_main,
+                                  ln_weight=n2.weight, ln_bias=n2.bias, eps=n2.eps)
+        if hasattr(m, "fc1"):
+            act = getattr(m, "act", None)
+            h = linear(y2, m.fc1.weight, m.fc1.bias, act="gelu", variant=v_main) if _is_erf_gelu(act) else act(linear(y2, m.fc1.weight, m.fc1.bias, variant=v_main))
+            fc2 = m.fc2
+        else:
+            h = linear(y2, m.w12.weight, m.w12.bias, act="swiglu", variant=v_main)
+            fc2 = m.w3
+        g2 = _gamma(block, "ls2")
+        if nxt is not None and _plain_ln(getattr(nxt, "norm1", None), C) and h.is_contiguous():
+            n1 = nxt.norm1
+            x, y = linear_layer_norm(h, fc2.weight, fc2.bias, res=x, gamma=g2, variant=v_fc2, ln_weight=n1.weight, ln_bias=n1.bias, eps=n1.eps)
+        else:
+            x, y = linear(h, fc2.weight, fc2.bias, res=x, gamma=g2, variant=v_fc2), None
+    return x
 
 
 def _dev_f16(t, numel=None):
@@ -160,7 +205,7 @@ def run_stack(blocks, x, attn_variant, gacc):
         _lib.check(lib.fbb_stack_forward_f16(descs, n, x.data_ptr(), B, N, scratch.data_ptr(), scratch.numel(),
                                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                                              _lib.stream_ptr(x.device)))
-    _lib.launched(7 * n)
+    _lib.launched(lib.fbb_stack_launches(descs, n, B * N))
     return True
 
 
@@ -324,8 +369,11 @@ class FastViT:
                 j = min(l for l in layers if l >= i)  # next selected layer
                 if not (use_runner and run_stack(self.blocks[i:j + 1], t, self.attn, self.gacc)):
                     use_runner = False
-                    for b in self.blocks[i:j + 1]:
-                        t = run_block(b, t, self.attn, self.gacc)
+                    if t.is_cuda:
+                        t = run_blocks_chained(self.blocks[i:j + 1], t, self.attn, self.gacc)
+                    else:
+                        for b in self.blocks[i:j + 1]:
+                            t = run_block(b, t, self.attn, self.gacc)
                 out.append(self._split_outputs(t, x, norm) if split else (_norm(self.vit.norm, t) if norm else t.clone()))
                 i = j + 1
         if os.environ.get("FBB_CHECK_STATUS") == "1" and not torch.cuda.is_current_stream_capturing():

@@ -121,6 +121,25 @@ int fbb_linear_f16(const void* A, const void* W, void* C, const void* bias, cons
                    int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate,
                    void* stream);
 
+/* fbb_linear_f16 (epilogue none or GELU) followed by the LayerNorm of the output rows: C as above, and
+ * y[m, :] = LayerNorm(C[m, :]) * ln_w + ln_b (fp16, row stride ldy; ln_w, ln_b: [N] fp16 or null). In one launch when the
+ * shape allows it (the CTA pairs that hold a row tile's columns form one thread-block cluster and exchange per-row
+ * statistics through distributed shared memory), otherwise as the GEMM followed by the LayerNorm kernel: the results are
+ * the same up to fp32 rounding of the statistics.
+ * Replaces: proj / fc2 with LayerScale + residual followed by norm2 of the same block / norm1 of the next block,
+ * fastbb/vit.py:116-118 + 126|130|139 and :137-143 + :114.
+ * counter: 4 bytes of device memory, zero when the call starts; every launch leaves it zero again, so one counter
+ * serves all calls on a stream (calls that may overlap on the GPU need different ones). It may be null when M is a
+ * multiple of 256 or has more than 8 rows beyond one; otherwise a null counter selects the two-launch form.
+ * y must not alias C; C may alias res. Requirements as for fbb_linear_f16, and ldy % 8 == 0. */
+int fbb_linear_layernorm_f16(const void* A, const void* W, void* C, const void* bias, const void* res, const void* gamma, int64_t M, int N,
+                             int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int epilogue, int accumulate, const void* ln_w,
+                             const void* ln_b, float ln_eps, void* y, int64_t ldy, void* counter, void* stream);
+
+/* Diagnostics: how many kernels fbb_linear_layernorm_f16 enqueues for this shape on the current device (1: fused, 2: the
+ * GEMM and the LayerNorm kernel, 0: nothing to do). No counterpart in the reference. */
+int fbb_linear_layernorm_launches(int64_t M, int N, int epilogue, int has_counter);
+
 /* O = softmax(scale . Q K^T) V for head dimension 64, no mask, any sequence length N >= 1.
  * Replaces: attention.attention + flash64_r{1,2}_{hh,fh,ff} (fastbb/attention.py:31-60,
  * fastbb/fastbb_kernels.cu:58-312) and the F.scaled_dot_product_attention fallback of fastbb/vit.py:149-150.
@@ -190,12 +209,16 @@ typedef struct fbb_block_desc {
     float scale;                   /* attention scale, > 0 */
 } fbb_block_desc;
 
-/* Bytes of scratch (LayerNorm output, packed qkv, attention output, MLP hidden) the blocks need for `tokens` = B*N tokens. */
+/* Bytes of scratch (LayerNorm output, packed qkv, attention output, MLP hidden, a counter) the blocks need for `tokens` = B*N tokens. */
 int64_t fbb_stack_scratch_bytes(const fbb_block_desc* blocks, int n_blocks, int64_t tokens);
+
+/* How many kernels fbb_stack_forward_f16 enqueues for this run on the current device (5 to 7 per block: each residual
+ * GEMM and the LayerNorm that follows it are one launch where fbb_linear_layernorm_f16 can fuse them). */
+int fbb_stack_launches(const fbb_block_desc* blocks, int n_blocks, int64_t tokens);
 
 /* x [B, N, C] fp16 contiguous is updated IN PLACE by n_blocks blocks (the residual epilogues write over their residual
  * input). scratch: 256-byte aligned device memory of at least fbb_stack_scratch_bytes(); workspace: optional, as for
- * fbb_flash64_f16_ws. Nothing is allocated; 7 * n_blocks kernels are enqueued on `stream`. */
+ * fbb_flash64_f16_ws. Nothing is allocated; fbb_stack_launches() kernels and one 256-byte memset are enqueued on `stream`. */
 int fbb_stack_forward_f16(const fbb_block_desc* blocks, int n_blocks, void* x, int B, int N, void* scratch, int64_t scratch_bytes,
                           void* workspace, int64_t workspace_bytes, void* stream);
 int fbb_block_forward_f16(const fbb_block_desc* block, void* x, int B, int N, void* scratch, int64_t scratch_bytes, void* workspace,

@@ -176,7 +176,7 @@ def test_linear_every_tile_form_matches_oracle(oracle, form, monkeypatch):
         pytest.skip("this device cannot co-schedule CTA pairs")
     g = torch.Generator().manual_seed(99)
     for M, N, K, act, variant in [(513, 1160, 200, "gelu", "f32"), (257, 384, 1536, None, "f32"), (1370, 1024, 264, "swiglu", "f32"),
-                                  (300, 520, 72, None, "h"), (1, 256, 64, None, "f32"), (264, 200, 136, "gelu", "h"), (776, 72, 64, None, "f32")]:
+                                  (300, 520, 72, None, "h"), (1, 256, 64, None, "f32"), (264, 200, 136, "gelu", "h"), (776, 72, 64, None, "f32"), (1032, 528, 72, "swiglu", "f32")]:
         x = torch.randn(M, K, generator=g).half()
         w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
         b = (0.1 * torch.randn(N, generator=g)).half()
@@ -270,6 +270,69 @@ def test_linear_full_size_linearity_and_column_sums(M, N, K):
     colsum = y1.double().sum(dim=1).cpu()
     want = (x1.cpu().double() @ w.cpu().double().sum(dim=0)) + b.cpu().double().sum()
     assert ((colsum - want).norm() / want.norm()) < 2e-3
+    status_ok()
+
+
+LINEAR_LN_CASES = [
+    # M, N, K, act, variant
+    (6145, 1024, 1024, None, "f32"), (6145, 1024, 4096, None, "h"), (4097, 768, 768, None, "f32"), (5480, 1536, 1536, None, "f32"),
+    (257, 384, 384, None, "f32"), (1370, 1024, 1024, None, "f32"), (520, 384, 1536, "gelu", "f32"), (300, 200, 64, None, "f32"),
+    (2056, 2048, 256, None, "f32"), (1, 64, 64, None, "f32"),
+]
+
+
+@pytest.mark.parametrize("M,N,K,act,variant", LINEAR_LN_CASES)
+def test_linear_layer_norm_matches_oracle(oracle, M, N, K, act, variant, monkeypatch):
+    """GEMM with the LayerScale + residual epilogue followed by the LayerNorm of its output rows, as one call: the GEMM
+    output against the oracle, the normalised rows against the oracle's LayerNorm of the fp16 output (what the separate
+    kernel would read), the one-launch form against the two-launch form, and the counter left at zero. Shapes cover the
+    fused form with one to four column chunks per row tile, remainder rows (M = 256 k + 1, + 8), and shapes that cannot
+    fuse (N not a multiple of 32, too many row tiles)."""
+    from fastbb_b200 import _lib
+    from fastbb_b200.attention import _counter
+    from fastbb_b200.gemm import linear_layer_norm
+    monkeypatch.setenv("FBB_LN_FUSION", "1")                    # the one-launch form is off by default (it measured slower)
+    g = torch.Generator().manual_seed(M + 3 * N + K)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+    b = (0.1 * torch.randn(N, generator=g)).half()
+    res = (torch.randn(M, N, generator=g) + 0.5).half()
+    gam = (0.05 + 0.15 * torch.rand(N, generator=g)).half()
+    lw, lb = (1 + 0.1 * torch.randn(N, generator=g)).half(), (0.1 * torch.randn(N, generator=g)).half()
+    d = lambda t: t.to(dev())  # noqa: E731
+    out, y = linear_layer_norm(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant=variant, ln_weight=d(lw), ln_bias=d(lb), eps=1e-6)
+    want = oracle.linear(x, w, b, act=act, res=res, gamma=gam)
+    tol = TOL_F16 if variant == "h" else TOL_F32
+    assert oracle.rel_l2(out.cpu().float(), want) < tol
+    assert oracle.rel_l2(y.cpu().float(), oracle.layer_norm(out.cpu(), lw, lb, 1e-6)) < TOL_F32   # LayerNorm of the fp16 rows the call wrote
+    assert int(_counter(dev())[0]) == 0
+    fused = _lib.load().fbb_linear_layernorm_launches(M, N, 1 if act == "gelu" else 0, 1) == 1
+    assert fused == (N % 32 == 0 and N <= 2048 and M < 74 * 256)
+    out_b, y_b = linear_layer_norm(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant=variant, ln_weight=d(lw), ln_bias=d(lb), eps=1e-6)
+    assert torch.equal(out_b, out) and torch.equal(y_b, y)      # again, same counter: identical
+    monkeypatch.setenv("FBB_GEMM_FORCE", "s256")                # a forced tile form also selects the two-launch path
+    out2, y2 = linear_layer_norm(d(x), d(w), d(b), act=act, res=d(res), gamma=d(gam), variant=variant, ln_weight=d(lw), ln_bias=d(lb), eps=1e-6)
+    assert oracle.rel_l2(out2.cpu().float(), out.cpu().float()) < 3e-4 and oracle.rel_l2(y2.cpu().float(), y.cpu().float()) < 1e-3
+    status_ok()
+
+
+@pytest.mark.parametrize("fusion", ["1", "0"])
+def test_linear_layer_norm_in_place_large_mean_and_no_affine(oracle, fusion, monkeypatch):
+    """In place on the residual stream (out is res), rows whose mean dwarfs their spread (the statistics are merged
+    chunk by chunk from two-pass partials, not taken from E[x^2] - E[x]^2), no LayerNorm parameters."""
+    from fastbb_b200.gemm import linear_layer_norm
+    monkeypatch.setenv("FBB_LN_FUSION", fusion)
+    g = torch.Generator().manual_seed(8)
+    M, N, K = 1281, 1024, 256
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / 16).half()
+    res = (torch.randn(M, N, generator=g) + 300.0).half()
+    rd = res.to(dev())
+    out, y = linear_layer_norm(x.to(dev()), w.to(dev()), None, res=rd, ln_weight=None, ln_bias=None, eps=1e-6, out=rd)
+    assert out.data_ptr() == rd.data_ptr()
+    want = oracle.linear(x, w, None, res=res)
+    assert oracle.rel_l2(out.cpu().float(), want) < TOL_F32
+    assert oracle.rel_l2(y.cpu().float(), oracle.layer_norm(out.cpu(), None, None, 1e-6)) < 2e-3
     status_ok()
 
 

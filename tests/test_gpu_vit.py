@@ -319,13 +319,15 @@ def test_host_pipeline_matches_direct_calls(oracle):
         pipe.result(tickets[0])
 
 
+@pytest.mark.parametrize("fusion", ["0", "1"])
 @pytest.mark.parametrize("arch,hw,spec", [("vits14", 224, "fh-g0"), ("vits14", 238, "hh-g1"), ("vits14", 224, "fh-g2"),
                                           ("vitg14", 224, "hh-g1")])
-def test_c_stack_runner_equals_per_operator_path(oracle, arch, hw, spec, monkeypatch):
+def test_c_stack_runner_equals_per_operator_path(oracle, arch, hw, spec, fusion, monkeypatch):
     """FastViT.run hands each run of blocks between selected layers to ONE C call (fbb_stack_forward_f16). It launches
     the same kernels in the same order as the per-operator path (FBB_NO_RUNNER=1), so the outputs must be identical
-    bit for bit, and both count 7 launches per block."""
+    bit for bit, and both count the same launches (5 to 7 per block: each residual GEMM carries the LayerNorm after it)."""
     from fastbb_b200 import _lib
+    monkeypatch.setenv("FBB_LN_FUSION", fusion)   # "1": each residual GEMM and the LayerNorm after it as one launch
     depth = 4 if arch == "vitg14" else None
     params, fast = _fast_model(oracle, arch, spec, **({"depth": depth} if depth else {}))
     x = oracle.make_image(2, hw, hw, seed=3).to("cuda:0")
@@ -350,7 +352,8 @@ def test_c_block_runner_direct_call_and_validation(oracle):
     params, fast = _fast_model(oracle, "vits14", "fh-g0")
     blk = fast.blocks[0]
     x = (0.5 * torch.randn(1, 300, 384, generator=torch.Generator().manual_seed(1))).half().to("cuda:0")
-    want = V.run_block(blk, x, "fh", False)
+    want = V.run_blocks_chained([blk], x, "fh", False)   # the per-operator path with the same launches as the runner
+    assert oracle.rel_l2(want.float().cpu(), V.run_block(blk, x, "fh", False).float().cpu()) < 1e-3   # = the plain seven-launch block
     d = _lib.BlockDesc()
     V._fill_block_desc(d, blk, "fh", False)
     lib = _lib.load()
