@@ -502,17 +502,22 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     tc_fence_after();
                     const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
                     const float cA = ex2_approx(mA - nA), cB = ex2_approx(mB - nB);
-                    uint32_t o[32];
-                    tmem_ld_16x256b_x8(tO, o);
-                    tmem_wait_ld();
+                    // in place, 16 columns at a time: this path is rare, and a whole O tile in registers on top of the
+                    // 64 scores held here would make the compiler spill in the hot loop around it
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[8];
+                        tmem_ld_16x256b_x2(tO + 16u * c, o);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA);
-                        o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA);
-                        o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB);
-                        o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB);
+                        for (int k = 0; k < 2; ++k) {
+                            o[4 * k] = __float_as_uint(__uint_as_float(o[4 * k]) * cA);
+                            o[4 * k + 1] = __float_as_uint(__uint_as_float(o[4 * k + 1]) * cA);
+                            o[4 * k + 2] = __float_as_uint(__uint_as_float(o[4 * k + 2]) * cB);
+                            o[4 * k + 3] = __float_as_uint(__uint_as_float(o[4 * k + 3]) * cB);
+                        }
+                        tmem_st_16x256b_x2(tO + 16u * c, o);
                     }
-                    tmem_st_16x256b_x8(tO, o);
                     lA *= cA;
                     lB *= cB;
                     mA = nA;

@@ -2,15 +2,21 @@
 // Replaces F.linear + the separate bias / GELU / SwiGLU / LayerScale-residual passes of fastbb/vit.py:114-143 and the
 // gemm_tn_* kernels of fastbb/fastbb_kernels.cu:323-446 (epilogue order bias -> act -> res + gamma*v, :418-427).
 //
-// Persistent kernel, one CTA per SM, 128 x BN output tiles per CTA, K consumed in 64-element (128-byte) blocks. Two forms:
-// one CTA per tile (cta_group::1), or a pair of CTAs (cluster of two, cta_group::2) on a 256 x BN tile, where each CTA
-// stages its 128 rows of A and BN/2 of the W rows and the leader CTA issues UMMAs that read both CTAs' shared memory
-// (no multicast load: each CTA fetches its own operands; only barrier signals cross the pair).
-//   warp 0      TMA producer: A box [64 x 128] and W box [64 x BN] per stage (128-byte swizzle, zero fill outside)
-//   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage into one of two tensor-memory accumulators
-//   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> shared staging tile -> TMA store
-// The two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
-// Both operands are K-major, so neither is transposed: nn.Linear's [N, K] weight is exactly the B operand.
+// K is consumed in 64-element (128-byte) blocks; both operands are K-major, so neither is transposed: nn.Linear's [N, K]
+// weight is exactly the B operand. Three forms, picked per shape by launch_linear's cost model:
+//   linear_umma_kernel<BN, SWIGLU, false>  persistent, one CTA per SM, 128 x BN output tiles (cta_group::1)
+//   linear_umma_kernel<BN, SWIGLU, true>   persistent, a pair of CTAs (cluster of two, cta_group::2) on a 256 x BN tile: each
+//                                          CTA stages its 128 rows of A and BN/2 of the W rows, the leader issues UMMAs that
+//                                          read both CTAs' shared memory
+//   linear_wide_pair_kernel                one pair per work item of 256 rows x w columns (w <= 512 in two accumulators), not
+//                                          persistent: for shapes with few tiles, where fixed tiles quantise badly; optionally
+//                                          with the LayerNorm of the output rows fused (clusters of up to four pairs)
+// No load is multicast: every CTA fetches its own operands with plain TMA loads; only barrier signals cross a pair.
+//   warp 0      TMA producer: A box [64 x 128] and the W boxes per stage (128-byte swizzle, zero fill outside)
+//   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage and accumulator
+//   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> shared staging tile -> TMA store;
+//               before that, the few rows beyond the last full row tile as dot products (remainder_rows_by_gemv)
+// In the persistent forms two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
 #include "common.cuh"
 #include <cstdlib>
 
@@ -867,6 +873,23 @@ static int remainder_rows(int64_t M, int tile_rows) {
 }
 static int64_t row_tiles(int64_t M, int tile_rows) { return remainder_rows(M, tile_rows) > 0 ? M / tile_rows : (M + tile_rows - 1) / tile_rows; }
 
+// Whether a persistent form leaves the remainder rows to its epilogue warps instead of giving them a row of tiles of their
+// own. Only when that saves a wave of tiles, and only when the dot products end well inside the grid's first tiles: each
+// warp takes ceil(dots / warps) of them at about 0.3 us + 0.45 us per 256 elements of K (a chain of L2 round trips), a
+// 256-column tile's main loop takes 0.37 us per k-block + 1 us. A small problem (M = 257: six CTAs, 48 warps, a spare SM
+// for every extra tile) keeps the extra tiles: there the dot products measured 5 - 9 us per launch slower.
+static bool remainder_by_gemv(int64_t M, int tile_rows, int64_t tiles_n, int workers, int64_t dots_per_row, int K, int bn) {
+    const int r = remainder_rows(M, tile_rows);
+    if (r == 0 || workers <= 0) return false;
+    const int64_t full = (M / tile_rows) * tiles_n, with_tiles = full + tiles_n;
+    if ((full + workers - 1) / workers == (with_tiles + workers - 1) / workers) return false;
+    const int64_t warps = (full < workers ? full : workers) * (tile_rows / BM) * 8;
+    const int64_t per_warp = (r * dots_per_row + warps - 1) / warps;
+    const double gemv_us = (double)per_warp * (0.3 + 0.45 * (double)((K + 255) / 256));
+    const double tile_us = (0.37 * (double)((K + BK - 1) / BK) + 1.0) * (double)bn / 256.0;
+    return gemv_us <= 2.0 * tile_us;
+}
+
 template <int BN, bool SWIGLU, bool CTA2>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmArgs g, cudaStream_t stream) {
     using S = GemmSmem<BN, CTA2>;
@@ -881,12 +904,13 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     }
     constexpr int kOutCols = SWIGLU ? BN / 2 : BN;
     constexpr int kTileRows = CTA2 ? 2 * BM : BM;
-    g.gemv_rows = remainder_rows(g.M, kTileRows);
-    g.tiles_m = (int)row_tiles(g.M, kTileRows);
-    g.gemv_row0 = g.gemv_rows > 0 ? g.tiles_m * kTileRows : g.M;
     g.tiles_n = (g.n_out + kOutCols - 1) / kOutCols;
-    const int tiles = g.tiles_m * g.tiles_n;
     const int workers_max = CTA2 ? max_pairs<BN, SWIGLU>() : num_sms();
+    const bool gemv = remainder_by_gemv(g.M, kTileRows, g.tiles_n, workers_max, SWIGLU ? 2 * g.n_out : g.n_out, g.K, BN);
+    g.gemv_rows = gemv ? remainder_rows(g.M, kTileRows) : 0;
+    g.tiles_m = (int)(gemv ? g.M / kTileRows : (g.M + kTileRows - 1) / kTileRows);
+    g.gemv_row0 = gemv ? g.tiles_m * kTileRows : g.M;
+    const int tiles = g.tiles_m * g.tiles_n;
     const int workers = tiles < workers_max ? tiles : workers_max;
     const int grid = CTA2 ? 2 * workers : workers;
     cudaError_t e = launch_pdl_cluster(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, CTA2 ? 2u : 1u, ta, tw, tc, g);
@@ -1130,16 +1154,22 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     const bool pairs_ok = gemm_pairs_enabled();
     const int pairs256 = pairs_ok ? (swiglu ? max_pairs<256, true>() : max_pairs<256, false>()) : 0;
     auto waves = [](int64_t tiles, int workers) { return (double)((tiles + workers - 1) / workers); };
-    const int64_t tm1 = row_tiles(M, BM), tm2 = row_tiles(M, 2 * BM);  // a remainder of a few rows gets no tile (remainder_rows_by_gemv)
     const int64_t tn256 = (g.n_out + 255) / 256, tn128 = (g.n_out + 127) / 128;
-    double best = waves(tm1 * tn256, sms) * 1.0;
+    const int64_t dots = swiglu ? 2 * g.n_out : g.n_out;
+    // row tiles of a form: a remainder of a few rows gets none where launch_variant will leave it to the epilogue warps
+    // (a SwiGLU tile of 256 weight rows yields 128 output columns)
+    auto row_tiles_of = [&](int tile_rows, int64_t tiles_n, int workers, int bn) {
+        const int64_t tn = swiglu ? tn128 : tiles_n;
+        return remainder_by_gemv(M, tile_rows, tn, workers, dots, (int)K, bn) ? M / tile_rows : (M + tile_rows - 1) / tile_rows;
+    };
+    double best = waves(row_tiles_of(BM, tn256, sms, 256) * tn256, sms) * 1.0;
     bool use_pairs = false, use128 = false;
     if (!swiglu) {
-        const double c = waves(tm1 * tn128, sms) * 0.60;
+        const double c = waves(row_tiles_of(BM, tn128, sms, 128) * tn128, sms) * 0.60;
         if (g.n_out <= 128 || c < best) { best = c; use128 = true; }
     }
     if (pairs256 > 0) {
-        const double c = waves(tm2 * tn256, pairs256) * 0.895 + (K < 1536 ? 0.7 : 0.2);
+        const double c = waves(row_tiles_of(2 * BM, tn256, pairs256, 256) * tn256, pairs256) * 0.895 + (K < 1536 ? 0.7 : 0.2);
         if (c < best) { best = c; use_pairs = true; use128 = false; }
     }
     // The wide pair form (items of w <= 512 columns, one wave): a candidate when every item fits on the device at once with

@@ -17,6 +17,7 @@ small-input configuration). The process-global cuBLAS fp16-accumulation flag the
 import ctypes
 import math
 import os
+import weakref
 
 import torch
 import torch.nn.functional as F
@@ -181,6 +182,54 @@ def _fill_block_desc(d, block, attn_variant, gacc):
 _ACC = {"f32": _lib.ACC_F32, "h": _lib.ACC_F16}
 
 
+class _CachedDesc:
+    """A filled fbb_block_desc of one block with what it was read from, so that a later call can tell cheaply whether it
+    still describes the block: the submodules and parameter tensors (by identity and device address) and the plain
+    attributes that went into it. Reading a block afresh costs ~20 us of Python (module attribute lookups); at ViT-S
+    sizes that was a third of an eager forward pass."""
+    __slots__ = ("desc", "mods", "params", "attrs", "cfg")
+
+    @staticmethod
+    def _attrs(block):
+        a, act = block.attn, getattr(block.mlp, "act", None)
+        return (a.num_heads, getattr(a, "scale", None), block.norm1.eps, block.norm2.eps, type(act), getattr(act, "approximate", None))
+
+    def __init__(self, block, attn_variant, gacc):
+        self.desc = _lib.BlockDesc()
+        _fill_block_desc(self.desc, block, attn_variant, gacc)
+        self.cfg = (attn_variant, gacc)
+        a, m = block.attn, block.mlp
+        leaves = [(block, n) for n in ("norm1", "norm2", "ls1", "ls2")] + [(a, "qkv"), (a, "proj")]
+        leaves += [(m, n) for n in (("fc1", "fc2", "act") if hasattr(m, "fc1") else ("w12", "w3"))]
+        self.mods = [(block, "attn", a), (block, "mlp", m)] + [(parent, n, parent._modules.get(n)) for parent, n in leaves]
+        self.params = [(leaf, n, t, None if t is None else t.data_ptr())
+                       for _, _, leaf in self.mods[2:] if leaf is not None for n, t in leaf._parameters.items()]
+        self.attrs = self._attrs(block)
+
+    def valid(self, block, attn_variant, gacc):
+        if self.cfg != (attn_variant, gacc):
+            return False
+        for parent, n, child in self.mods:
+            if parent._modules.get(n) is not child:
+                return False
+        for leaf, n, t, ptr in self.params:
+            if leaf._parameters.get(n) is not t or (t is not None and t.data_ptr() != ptr):
+                return False
+        return self.attrs == self._attrs(block)
+
+
+def _block_desc(block, attn_variant, gacc):
+    """The block's fbb_block_desc, read afresh only when the block changed since the last call (raises like
+    _fill_block_desc)."""
+    ent = _DESCS.get(block)
+    if ent is None or not ent.valid(block, attn_variant, gacc):
+        ent = _DESCS[block] = _CachedDesc(block, attn_variant, gacc)
+    return ent.desc
+
+
+_DESCS = weakref.WeakKeyDictionary()  # block module -> _CachedDesc (kept outside the module: nothing to copy or pickle)
+
+
 def run_stack(blocks, x, attn_variant, gacc):
     """blocks[...] applied IN PLACE to x [B, N, C] (fp16, contiguous, CUDA) through ONE call of the C stack runner
     (fbb_stack_forward_f16: 7 launches per block, the same kernels in the same order as run_block). Returns False
@@ -188,8 +237,8 @@ def run_stack(blocks, x, attn_variant, gacc):
     n = len(blocks)
     descs = (_lib.BlockDesc * n)()
     try:
-        for d, b in zip(descs, blocks):
-            _fill_block_desc(d, b, attn_variant, gacc)
+        for i, b in enumerate(blocks):
+            descs[i] = _block_desc(b, attn_variant, gacc)
     except (LookupError, AttributeError):
         return False
     if not (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() == 3 and x.shape[2] == descs[0].C):

@@ -344,6 +344,60 @@ def test_c_stack_runner_equals_per_operator_path(oracle, arch, hw, spec, fusion,
     assert _lib.device_status() == (0, 0, 0, 0)
 
 
+def _lib_status():
+    from fastbb_b200 import _lib
+    return _lib.device_status()
+
+
+def test_runner_descriptor_cache_follows_the_block(oracle):
+    """The C runner's cached block descriptors are re-read when a block changes: a parameter replaced by a new object,
+    its storage swapped through .data, a submodule replaced, eps changed, and a weight edited in place (same storage:
+    nothing to re-read, the kernel sees it). Each time the runner equals the per-operator path bit for bit."""
+    from fastbb_b200 import vit as V
+    params, fast = _fast_model(oracle, "vits14", "fh-g0")
+    blk = fast.blocks[0]
+    x = (0.5 * torch.randn(1, 300, 384, generator=torch.Generator().manual_seed(2))).half().to("cuda:0")
+
+    def runner():
+        y = x.clone()
+        assert V.run_stack([blk], y, "fh", False)
+        return y
+
+    def check():
+        got, want = runner(), V.run_blocks_chained([blk], x, "fh", False)
+        assert torch.equal(got, want)
+        return got
+
+    first = check()
+    assert V._DESCS[blk].valid(blk, "fh", False)
+    ent = V._DESCS[blk]
+    assert torch.equal(runner(), first) and V._DESCS[blk] is ent           # unchanged block: the cached descriptor is used
+    with torch.no_grad():
+        blk.attn.qkv.weight.mul_(0.5)                                      # in place: same storage
+    second = check()
+    assert V._DESCS[blk] is ent and not torch.equal(second, first)
+    blk.attn.proj.weight = torch.nn.Parameter(blk.attn.proj.weight.detach().clone() * 0.5, requires_grad=False)
+    third = check()
+    assert V._DESCS[blk] is not ent and not torch.equal(third, second)
+    ent = V._DESCS[blk]
+    blk.mlp.fc2.bias.data = blk.mlp.fc2.bias.data.clone() + 0.25            # new storage behind the same Parameter
+    fourth = check()
+    assert V._DESCS[blk] is not ent and not torch.equal(fourth, third)
+    ent = V._DESCS[blk]
+    blk.norm2 = torch.nn.LayerNorm(384, eps=1e-6).half().to("cuda:0")      # a fresh module
+    torch.nn.init.constant_(blk.norm2.weight, 0.5)
+    fifth = check()
+    assert V._DESCS[blk] is not ent and not torch.equal(fifth, fourth)
+    ent = V._DESCS[blk]
+    blk.norm1.eps = 1e-2
+    check()
+    assert V._DESCS[blk] is not ent
+    assert not V._DESCS[blk].valid(blk, "hh", False)                        # another attention variant: read afresh
+    blk.attn.qkv.weight.data = blk.attn.qkv.weight.data.float()            # no longer fp16: outside what the runner covers
+    assert V.run_stack([blk], x.clone(), "fh", False) is False
+    assert _lib_status() == (0, 0, 0, 0)
+
+
 def test_c_block_runner_direct_call_and_validation(oracle):
     """fbb_block_forward_f16 through ctypes on one block: equals run_block, updates x in place, rejects a scratch that is
     too small, a head count that does not match C, and a null weight."""

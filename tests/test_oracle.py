@@ -48,6 +48,32 @@ def test_block_stack_c2_timm_like(oracle):
     assert abs(float(y.double().norm()) / float(g["out_norm"]) - 1) < 1e-5
 
 
+def test_block_stack_c2_at_4097_tokens_one_image_of_the_batch_fixture(oracle):
+    """The full-size c2 fixture (4097 tokens, batch 8) also pins the oracle: image 5 of the batch, run on its own."""
+    g = load_golden("c2_vitb16_blocks_4097_b8")
+    params = oracle.make_params("vitb16_timm", seed=0, layerscale=False, patch_size=16, img_size=224)
+    tokens = torch.randn(8, 4097, 768, generator=torch.Generator().manual_seed(1))
+    assert_same_inputs(g["tokens_checksum"], tokens, "tokens")
+    y = oracle.block_stack(params, tokens[5:6], 12)
+    assert oracle.rel_l2(y[:, ::int(g["token_stride"])], torch.from_numpy(g["out"][5:6])) < FP32_TOL
+    assert abs(float(y.double().norm()) / float(g["out_norm_per_image"][5]) - 1) < 1e-5
+
+
+def test_stack_c3_batch4_fixture_one_image(oracle):
+    """The batch-4 c3 fixture against the oracle on image 2 of the batch (the images of a batch are independent)."""
+    g = load_golden("c3_vitg14_518_b4")
+    params = oracle.make_params("vitg14", seed=0)
+    x = oracle.make_image(4, 518, 518, seed=1)
+    assert_same_inputs(g["image_checksum"], x, "image")
+    layers = [int(i) for i in g["layers"]]
+    stride = int(g["token_stride"])
+    outs = oracle.get_intermediate_layers(params, x[2:3], layers, 24, return_class_token=True)
+    for i, (patch, cls) in zip(layers, outs):
+        assert oracle.rel_l2(patch[:, ::stride], torch.from_numpy(g[f"patch_{i}"][2:3])) < FP32_TOL
+        assert oracle.rel_l2(cls, torch.from_numpy(g[f"cls_{i}"][2:3])) < FP32_TOL
+        assert abs(float(patch.double().norm()) / float(g[f"patch_norm_per_image_{i}"][2]) - 1) < 1e-5
+
+
 def _op_inputs():
     """Same generator sequence as make_golden.py."""
     g = torch.Generator().manual_seed(7)
