@@ -459,25 +459,46 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-// Exact (erf) GELU, branch-free: x * Phi(x) with Phi from the complementary error function of |x| / sqrt(2) in the
-// rational-times-Gaussian form erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2), t = 1 / (1 + p z)
-// (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7). Working from erfc keeps the negative tail accurate (no 1 - erf
-// cancellation): x > 0 -> x - x q, x <= 0 -> x q with q = erfc(z) / 2. Against float64 erf-GELU: max abs error 3.3e-7,
-// i.e. far below one fp16 rounding of the result. One reciprocal, one ex2 and nine FMAs instead of erff's two divergent
-// branches: the GELU epilogue of a 128 x 256 tile must stay shorter than the tile's main loop (K = 1024: 8.3 k clocks).
-__device__ __forceinline__ float gelu_erf(float x) {
-    const float z = fabsf(x) * 0.70710678118654752440f;
-    float t;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
-    const float e = ex2_approx(x * x * -0.72134752044448170368f);  // exp(-z^2)
-    float q = fmaf(1.061405429f, t, -1.453152027f);
-    q = fmaf(q, t, 1.421413741f);
-    q = fmaf(q, t, -0.284496736f);
-    q = fmaf(q, t, 0.254829592f);
-    q = 0.5f * q * t * e;
-    const float xq = x * q;
-    return x > 0.f ? x - xq : xq;
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
 }
+// Exact (erf) GELU, branch-free, for a pair of values: x * Phi(x) with Phi from the complementary error function of
+// z = |x| / sqrt(2) in the form erfc(z) = (1 + a1 z + ... + a6 z^6)^-16 (Abramowitz & Stegun 7.1.28, |error| <= 3e-7).
+// With the coefficients scaled by 2^(1/16) the sixteenth power is 2 / erfc(z), so one reciprocal gives q = erfc(z) / 2 and
+// x > 0 -> x - x q, x <= 0 -> x q, i.e. max(x, 0) - |x q| (no 1 - erf cancellation in the negative tail; a power that
+// overflows gives q = 0, the right limit). Against float64 erf-GELU: max abs error 7.1e-7 over [-12, 12], below 1e-2 of an
+// fp16 rounding of the result except around x = -4 (results ~1e-4, up to 8 fp16 steps). Six packed FMAs, five packed
+// multiplies and ONE transcendental (the reciprocal) per value: the form with exp(-z^2) needed two, and the 16-lane
+// transcendental unit is what the GELU epilogue of a 128 x 256 tile waits for.
+__device__ __forceinline__ float2 gelu_erf2(float2 x) {
+    const float2 z = make_float2(fabsf(x.x) * 0.70710678118654752440f, fabsf(x.y) * 0.70710678118654752440f);
+    float2 p = ffma2(z, make_float2(4.49703984e-05f, 4.49703984e-05f), make_float2(0.000288811862f, 0.000288811862f));
+    p = ffma2(p, z, make_float2(0.000158744544f, 0.000158744544f));
+    p = ffma2(p, z, make_float2(0.00968096871f, 0.00968096871f));
+    p = ffma2(p, z, make_float2(0.0441539958f, 0.0441539958f));
+    p = ffma2(p, z, make_float2(0.0736454055f, 0.0736454055f));
+    p = ffma2(p, z, make_float2(1.04427373f, 1.04427373f));
+    p = fmul2(p, p);
+    p = fmul2(p, p);
+    p = fmul2(p, p);
+    p = fmul2(p, p);
+    float2 q;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q.x) : "f"(p.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q.y) : "f"(p.y));
+    const float2 h = fmul2(x, q);
+    return make_float2(fmaxf(x.x, 0.f) - fabsf(h.x), fmaxf(x.y, 0.f) - fabsf(h.y));
+}
+__device__ __forceinline__ float gelu_erf(float x) { return gelu_erf2(make_float2(x, x)).x; }
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
 }  // namespace fbb

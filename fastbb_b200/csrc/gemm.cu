@@ -16,7 +16,8 @@
 //   warp 1      UMMA issuer: 4 x tcgen05.mma (K = 16 each) per stage and accumulator
 //   warps 2..9  epilogue: tcgen05.ld -> bias -> GELU | SwiGLU -> gamma*v + res -> fp16 -> shared staging tile -> TMA store;
 //               before that, the few rows beyond the last full row tile as dot products (remainder_rows_by_gemv)
-// In the persistent forms two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// In the persistent forms two accumulators (2 x BN columns) let the epilogue of tile i overlap the main loop of tile i+1;
+// the plain 256-column form cuts the tiles of a partly filled second wave into 128- or 64-column slices (narrow_tail).
 #include "common.cuh"
 #include <cstdlib>
 
@@ -62,6 +63,9 @@ struct GemmArgs {
     const __half* W;
     int64_t lda, ldw;
     int gemv_row0, gemv_rows;
+    // The last, partly filled wave of tiles may be cut into narrower items so that every CTA gets one (see narrow_tail):
+    // items [0, wide_tiles) are whole tiles, the next narrow_tiles items are narrow_w-column slices of the tiles after them.
+    int wide_tiles, narrow_w, narrow_tiles;
 };
 
 // The few rows beyond the last full row tile (every ViT token count is a multiple of the tile height plus the cls token:
@@ -117,7 +121,7 @@ __device__ __forceinline__ void remainder_rows_by_gemv(const GemmArgs& g, bool s
 template <int BN, bool SWIGLU, bool CTA2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                   const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
+                   const __grid_constant__ CUtensorMap tmap_wn, const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
     using S = GemmSmem<BN, CTA2>;
     // pair geometry: rank 0 (the leader) issues the UMMAs; work items are 256-row tiles shared by the pair
     const uint32_t rank = CTA2 ? cluster_ctarank() : 0u;
@@ -142,7 +146,22 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_kb = (g.K + BK - 1) / BK;
-    const int num_tiles = g.tiles_m * g.tiles_n;
+    // Work items: whole tiles, then (plain single-CTA 256-column form only) the slices of the last wave's tiles. Every role
+    // walks the same list: m0 = first row (of this CTA), n0 = first output column, w = W rows (= columns) of the item.
+    constexpr bool kNarrowOk = !SWIGLU && !CTA2 && BN == 256;
+    const int num_items = g.wide_tiles + (kNarrowOk ? g.narrow_tiles : 0);
+    auto item_at = [&](int idx, int& m0, int& n0, int& w) {
+        int tile = idx, sub = 0;
+        w = BN;
+        if (kNarrowOk && idx >= g.wide_tiles) {
+            const int per = BN / g.narrow_w, j = idx - g.wide_tiles;
+            tile = g.wide_tiles + j / per;
+            sub = j - (j / per) * per;
+            w = g.narrow_w;
+        }
+        m0 = (tile / g.tiles_n) * kTileRows + (int)rank * BM;
+        n0 = (tile % g.tiles_n) * kOutCols + sub * g.narrow_w;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -183,9 +202,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-                const int m0 = (tile / g.tiles_n) * kTileRows + (int)rank * BM;
-                const int nt = tile % g.tiles_n;
+            for (int item = worker; item < num_items && ok; item += num_workers) {
+                int m0, n0, w;
+                item_at(item, m0, n0, w);
+                const int nt = n0 / kOutCols;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, s_abort, DEV_TIMEOUT_SMEM_EMPTY, s)) { ok = false; break; }
                     const uint32_t sa = base + s * S::kStageBytes;
@@ -197,6 +217,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         tma_load_2d_pair(sa, &tmap_a, full_bar(s), kb * BK, m0);
                         const int wrow = SWIGLU ? (rank == 0 ? nt * (BN / 2) : g.N / 2 + nt * (BN / 2)) : nt * BN + (int)rank * (BN / 2);
                         tma_load_2d_pair(sb, &tmap_w, full_bar(s), kb * BK, wrow);
+                    } else if (kNarrowOk && w != BN) {
+                        // a slice: its W rows in 64-row boxes, laid out like the first rows of a whole tile's box
+                        mbar_arrive_expect_tx(full_bar(s), (uint32_t)(S::kABytes + w * BK * 2));
+                        tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, m0);
+                        for (int r = 0; r < w; r += 64) tma_load_2d(sb + (uint32_t)(r * BK * 2), &tmap_wn, full_bar(s), kb * BK, n0 + r);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
                         tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, m0);
@@ -217,7 +242,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // ------------------------------------------------------------------ UMMA issuer (the leader CTA of a pair only)
         // The whole warp runs this loop and one elected lane issues each instruction, so that descriptors and
         // addresses are warp-uniform values (uniform registers) rather than per-thread arithmetic in a divergent branch.
-        const uint32_t idesc = make_idesc_f16(kTileRows, BN, !g.acc_f16, false, false);
+        const uint32_t idesc_tile = make_idesc_f16(kTileRows, BN, !g.acc_f16, false, false);
+        const uint32_t idesc_slice = make_idesc_f16(kTileRows, (kNarrowOk && g.narrow_w > 0) ? g.narrow_w : BN, !g.acc_f16, false, false);
         constexpr uint64_t desc_hi = make_smem_desc_hi(16, 1024);
         const uint64_t adesc0 = smem_desc(base, desc_hi);
         auto all_ok = [&](bool mine) { return __all_sync(0xffffffffu, mine) != 0; };
@@ -226,7 +252,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+        for (int item = worker; item < num_items && ok; item += num_workers) {
+            const uint32_t idesc = (kNarrowOk && item >= g.wide_tiles) ? idesc_slice : idesc_tile;
             if (!all_ok(mbar_wait(tempty_bar(acc), acc_ph ^ 1u, s_abort, DEV_TIMEOUT_TMEM_EMPTY, acc))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -264,14 +291,15 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         if (g.gemv_rows > 0) remainder_rows_by_gemv(g, SWIGLU, (int)blockIdx.x * 8 + ew, (int)gridDim.x * 8, lane);
         int acc = 0;
         uint32_t acc_ph = 0;
-        for (int tile = worker; tile < num_tiles; tile += num_workers) {
-            const int m0 = (tile / g.tiles_n) * kTileRows + (int)rank * BM;
-            const int nt = tile % g.tiles_n;
-            const int n0 = nt * kOutCols;  // first output column of the tile
-            // stage bias (W-row indexed) and gamma (output-column indexed) for this tile
+        for (int item = worker; item < num_items; item += num_workers) {
+            int m0, n0, w;  // n0: first output column of the item
+            item_at(item, m0, n0, w);
+            const int half_cols = SWIGLU ? kOutCols / 2 : w / 2;  // output columns per half of the epilogue warps
+            const int chunks = half_cols / 32;
+            // stage bias (W-row indexed) and gamma (output-column indexed) for this item
             float* s_bias = s_params + acc * 2 * BN;
             float* s_gamma = s_bias + BN;
-            for (int i = et; i < BN; i += kEpiThreads) {
+            for (int i = et; i < w; i += kEpiThreads) {
                 int wrow;
                 if (SWIGLU) wrow = i < BN / 2 ? n0 + i : g.N / 2 + n0 + (i - BN / 2);
                 else wrow = n0 + i;
@@ -291,9 +319,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             if constexpr (!SWIGLU) {
 #pragma unroll
                 for (int ci = 0; ci < kChunks; ++ci) {
+                    if (ci >= chunks) break;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int col = n0 + chalf * (kOutCols / 2) + ci * 32 + q * 8;
+                        const int col = n0 + chalf * half_cols + ci * 32 + q * 8;
                         rr[ci][q] = (r_row != nullptr && row_ok && col < g.n_out) ? *reinterpret_cast<const uint4*>(r_row + col) : make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
@@ -303,7 +332,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll
             for (int ci = 0; ci < kChunks; ++ci) {
-                const int c0 = chalf * (kOutCols / 2) + ci * 32;
+                if (ci >= chunks) break;
+                const int c0 = chalf * half_cols + ci * 32;
                 uint32_t r[32];
                 float v[32];
                 tmem_ld32(t_row + (uint32_t)c0, r);
@@ -330,7 +360,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     for (int j = 0; j < 32; ++j) v[j] += s_bias[c0 + j];
                     if (g.act == 1) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                        for (int j = 0; j < 32; j += 2) {
+                            const float2 y = gelu_erf2(make_float2(v[j], v[j + 1]));
+                            v[j] = y.x;
+                            v[j + 1] = y.y;
+                        }
                     }
                 }
                 // residual + LayerScale (columns beyond n_out and rows beyond M hold zeros and are clipped by the store)
@@ -690,7 +724,11 @@ linear_wide_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (int j = 0; j < 32; ++j) v[j] += s_bias[c0 + j];
                 if (g.act == 1) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                    for (int j = 0; j < 32; j += 2) {
+                        const float2 y = gelu_erf2(make_float2(v[j], v[j + 1]));
+                        v[j] = y.x;
+                        v[j + 1] = y.y;
+                    }
                 }
                 if (g.res != nullptr) {
 #pragma unroll
@@ -890,8 +928,34 @@ static bool remainder_by_gemv(int64_t M, int tile_rows, int64_t tiles_n, int wor
     return gemv_us <= 2.0 * tile_us;
 }
 
+// A launch of between one and two waves of tiles leaves most SMs idle for half of its time (M = 1370, N = 4096: 176 tiles =
+// 148 + 28). The plain single-CTA 256-column form then cuts the tiles of the second wave into slices of 128 or 64 columns,
+// as narrow as it takes for every slice to run at once: a slice costs more per column (the A tile is loaded for fewer
+// columns: about 0.62 / 0.45 of a whole tile's time) but the launch ends that much earlier (measured 21.4 -> 16 - 19 us
+// for that shape). With two or more full waves before it the partial wave is cheap as it is - its few tiles run faster
+// than tiles of a full wave, which share the L2-to-SM bandwidth - and slices measured slower (M = 6145, N = 4096: 46.4
+// against 45.7 us; M = 16385: 127 against 118), so they are not used there.
+// Returns the slice width (0: none) and its cost in tile times.
+static int narrow_tail(int64_t tiles, int workers, double* cost) {
+    if (cost != nullptr) *cost = 0.0;
+    const char* f = getenv("FBB_GEMM_NARROW");  // 0 | 64 | 128: tuning and test override, read per call
+    const int forced = f != nullptr ? atoi(f) : -1;
+    if (workers <= 0 || tiles <= workers || forced == 0) return 0;
+    const int64_t rest = tiles % workers;
+    if (rest == 0) return 0;
+    int w = 0;
+    if (tiles / workers == 1) {
+        if (rest * 4 <= workers) w = 64;
+        else if (rest * 2 <= workers) w = 128;
+    }
+    if (forced == 64 || forced == 128) w = rest * (256 / forced) <= workers ? forced : 0;
+    if (cost != nullptr) *cost = w == 64 ? 0.45 : (w == 128 ? 0.62 : 1.0);
+    return w;
+}
+
 template <int BN, bool SWIGLU, bool CTA2>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, GemmArgs g, cudaStream_t stream) {
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& twn, const CUtensorMap& tc, GemmArgs g,
+                          cudaStream_t stream) {
     using S = GemmSmem<BN, CTA2>;
     static bool configured[64] = {};
     int dev = 0;
@@ -913,7 +977,16 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     const int tiles = g.tiles_m * g.tiles_n;
     const int workers = tiles < workers_max ? tiles : workers_max;
     const int grid = CTA2 ? 2 * workers : workers;
-    cudaError_t e = launch_pdl_cluster(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, CTA2 ? 2u : 1u, ta, tw, tc, g);
+    g.wide_tiles = tiles;
+    g.narrow_w = g.narrow_tiles = 0;
+    if constexpr (!SWIGLU && !CTA2 && BN == 256) {
+        g.narrow_w = narrow_tail(tiles, workers_max, nullptr);
+        if (g.narrow_w > 0) {
+            g.wide_tiles = tiles - tiles % workers_max;
+            g.narrow_tiles = (tiles - g.wide_tiles) * (BN / g.narrow_w);
+        }
+    }
+    cudaError_t e = launch_pdl_cluster(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, CTA2 ? 2u : 1u, ta, tw, twn, tc, g);
     if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel launch: %s", cudaGetErrorString(e));
     return FBB_OK;
 }
@@ -1162,7 +1235,12 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
         const int64_t tn = swiglu ? tn128 : tiles_n;
         return remainder_by_gemv(M, tile_rows, tn, workers, dots, (int)K, bn) ? M / tile_rows : (M + tile_rows - 1) / tile_rows;
     };
-    double best = waves(row_tiles_of(BM, tn256, sms, 256) * tn256, sms) * 1.0;
+    double best;
+    {
+        const int64_t t256 = row_tiles_of(BM, tn256, sms, 256) * tn256;
+        double tail = 0.0;
+        best = (!swiglu && narrow_tail(t256, sms, &tail) > 0) ? (double)(t256 / sms) + tail : waves(t256, sms) * 1.0;
+    }
     bool use_pairs = false, use128 = false;
     if (!swiglu) {
         const double c = waves(row_tiles_of(BM, tn128, sms, 128) * tn128, sms) * 0.60;
@@ -1225,6 +1303,12 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     uint32_t box_w[2] = {BK, use_pairs && !swiglu ? w_rows / 2 : w_rows};
     st = make_tmap_f16(&tw, W, 2, dims_w, str_w, box_w);
     if (st != FBB_OK) return st;
+    CUtensorMap twn = tw;  // 64-row boxes of W for the slices of the last wave (plain 256-column form only)
+    if (!swiglu && !use_pairs && !use128) {
+        uint32_t box_wn[2] = {BK, 64};
+        st = make_tmap_f16(&twn, W, 2, dims_w, str_w, box_wn);
+        if (st != FBB_OK) return st;
+    }
 
     CUtensorMap tc;
     uint64_t dims_c[2] = {(uint64_t)g.n_out, (uint64_t)M};
@@ -1234,13 +1318,13 @@ int launch_linear(const void* A, const void* W, void* C, const void* bias, const
     if (st != FBB_OK) return st;
 
     if (use_pairs) {
-        if (swiglu) return launch_variant<256, true, true>(ta, tw, tc, g, stream);
-        if (use128) return launch_variant<128, false, true>(ta, tw, tc, g, stream);
-        return launch_variant<256, false, true>(ta, tw, tc, g, stream);
+        if (swiglu) return launch_variant<256, true, true>(ta, tw, twn, tc, g, stream);
+        if (use128) return launch_variant<128, false, true>(ta, tw, twn, tc, g, stream);
+        return launch_variant<256, false, true>(ta, tw, twn, tc, g, stream);
     }
-    if (swiglu) return launch_variant<256, true, false>(ta, tw, tc, g, stream);
-    if (use128) return launch_variant<128, false, false>(ta, tw, tc, g, stream);
-    return launch_variant<256, false, false>(ta, tw, tc, g, stream);
+    if (swiglu) return launch_variant<256, true, false>(ta, tw, twn, tc, g, stream);
+    if (use128) return launch_variant<128, false, false>(ta, tw, twn, tc, g, stream);
+    return launch_variant<256, false, false>(ta, tw, twn, tc, g, stream);
 }
 
 }  // namespace fbb

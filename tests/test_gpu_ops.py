@@ -192,6 +192,38 @@ def test_linear_every_tile_form_matches_oracle(oracle, form, monkeypatch):
     status_ok()
 
 
+@pytest.mark.parametrize("M,N,K,act,variant", [(2561, 2000, 136, "gelu", "f32"), (2561, 1848, 72, None, "h"), (6145, 1024, 64, None, "f32"),
+                                                (2600, 2048, 200, None, "f32")])
+def test_linear_last_wave_in_slices_equals_whole_tiles(oracle, M, N, K, act, variant, monkeypatch):
+    """The persistent 256-column form cuts the tiles of a partly filled second wave into 128- or 64-column slices (168
+    to 196 tiles on 148 SMs here, with ragged last rows and columns, and slices that lie wholly beyond N). Each width, and the rule's own choice, must give the oracle's result and, element for element, the bits
+    of the launch without slices (every output element sees the same K loop)."""
+    from fastbb_b200.gemm import linear
+    monkeypatch.setenv("FBB_GEMM_FORCE", "s256")
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+    b = (0.1 * torch.randn(N, generator=g)).half()
+    res = torch.randn(M, N, generator=g).half() if act is None else None
+    gam = (0.05 + 0.15 * torch.rand(N, generator=g)).half() if act is None else None
+    want = oracle.linear(x, w, b, act=act, res=res, gamma=gam)
+    d = lambda t: None if t is None else t.to(dev())  # noqa: E731
+    xd, wd, bd, rd, gd = d(x), d(w), d(b), d(res), d(gam)
+    outs = {}
+    for width in ["0", "64", "128", None]:
+        if width is None:
+            monkeypatch.delenv("FBB_GEMM_NARROW", raising=False)
+        else:
+            monkeypatch.setenv("FBB_GEMM_NARROW", width)
+        out, check = padded((M, N))
+        outs[width] = linear(xd, wd, bd, act=act, res=rd, gamma=gd, variant=variant, out=out).clone()
+        check()
+        assert oracle.rel_l2(outs[width].cpu().float(), want) < (TOL_F16 if variant == "h" else TOL_F32), width
+    for width in ["64", "128", None]:
+        assert torch.equal(outs[width], outs["0"]), width
+    status_ok()
+
+
 def test_linear_against_reference_outputs(oracle):
     """Same seeded inputs as tests/golden/make_golden.py; the stored outputs come from the reference's gemm.linear."""
     from fastbb_b200.gemm import linear
