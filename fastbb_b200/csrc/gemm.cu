@@ -118,7 +118,7 @@ __device__ __forceinline__ void remainder_rows_by_gemv(const GemmArgs& g, bool s
     }
 }
 
-template <int BN, bool SWIGLU, bool CTA2>
+template <int BN, bool SWIGLU, bool CTA2, bool SLICES = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_wn, const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
@@ -148,7 +148,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int num_kb = (g.K + BK - 1) / BK;
     // Work items: whole tiles, then (plain single-CTA 256-column form only) the slices of the last wave's tiles. Every role
     // walks the same list: m0 = first row (of this CTA), n0 = first output column, w = W rows (= columns) of the item.
-    constexpr bool kNarrowOk = !SWIGLU && !CTA2 && BN == 256;
+    static_assert(!SLICES || (!SWIGLU && !CTA2 && BN == 256), "slices: plain single-CTA 256-column form only");
+    constexpr bool kNarrowOk = SLICES;  // without slices every width below is a compile-time constant
     const int num_items = g.wide_tiles + (kNarrowOk ? g.narrow_tiles : 0);
     auto item_at = [&](int idx, int& m0, int& n0, int& w) {
         int tile = idx, sub = 0;
@@ -963,6 +964,10 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
     auto kern = linear_umma_kernel<BN, SWIGLU, CTA2>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+        if constexpr (!SWIGLU && !CTA2 && BN == 256) {
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(linear_umma_kernel<BN, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+        }
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(linear_umma_kernel): %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
@@ -984,6 +989,12 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tw, const CU
         if (g.narrow_w > 0) {
             g.wide_tiles = tiles - tiles % workers_max;
             g.narrow_tiles = (tiles - g.wide_tiles) * (BN / g.narrow_w);
+            // the instantiation whose item widths are run-time values (measured 2 - 7 % slower on whole tiles, which is
+            // why launches without slices do not use it)
+            cudaError_t e = launch_pdl_cluster(linear_umma_kernel<BN, false, false, true>, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream,
+                                               1u, ta, tw, twn, tc, g);
+            if (e != cudaSuccess) return fail((int)e, "linear_umma_kernel (slices) launch: %s", cudaGetErrorString(e));
+            return FBB_OK;
         }
     }
     cudaError_t e = launch_pdl_cluster(kern, dim3(grid), dim3(kGemmThreads), S::kDynamic, stream, CTA2 ? 2u : 1u, ta, tw, twn, tc, g);
