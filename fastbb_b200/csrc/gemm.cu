@@ -932,7 +932,8 @@ static bool remainder_by_gemv(int64_t M, int tile_rows, int64_t tiles_n, int wor
 // A launch of between one and two waves of tiles leaves most SMs idle for half of its time (M = 1370, N = 4096: 176 tiles =
 // 148 + 28). The plain single-CTA 256-column form then cuts the tiles of the second wave into slices of 128 or 64 columns,
 // as narrow as it takes for every slice to run at once: a slice costs more per column (the A tile is loaded for fewer
-// columns: about 0.62 / 0.45 of a whole tile's time) but the launch ends that much earlier (measured 21.4 -> 16 - 19 us
+// columns: charged 0.85 / 0.45 of a whole tile's time, fitted so that M = 6145, N = 1024, K = 1024 keeps the wide pair
+// form, 15.4 us against 16.1 us with 128-column slices) but the launch ends that much earlier (measured 21.4 -> 15 - 16 us
 // for that shape). With two or more full waves before it the partial wave is cheap as it is - its few tiles run faster
 // than tiles of a full wave, which share the L2-to-SM bandwidth - and slices measured slower (M = 6145, N = 4096: 46.4
 // against 45.7 us; M = 16385: 127 against 118), so they are not used there.
@@ -950,7 +951,7 @@ static int narrow_tail(int64_t tiles, int workers, double* cost) {
         else if (rest * 2 <= workers) w = 128;
     }
     if (forced == 64 || forced == 128) w = rest * (256 / forced) <= workers ? forced : 0;
-    if (cost != nullptr) *cost = w == 64 ? 0.45 : (w == 128 ? 0.62 : 1.0);
+    if (cost != nullptr) *cost = w == 64 ? 0.45 : (w == 128 ? 0.85 : 1.0);
     return w;
 }
 
