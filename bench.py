@@ -432,6 +432,17 @@ def run_ours(args, rank, local_rank, world):
         }
         if configs is not None:
             line["configs"] = configs
+        if world == 1 and not args.no_reference_gpu:
+            # For context, after everything of this library has been timed: the same workload through the reference's own
+            # GPU tier (its mma.sync kernels recompiled for this GPU, from oracle/_ref). Not the reference arm, which is
+            # `--impl reference`.
+            try:
+                import bench_configs as BC
+                torch.cuda.empty_cache()
+                spec = args.spec[:-6] if args.spec.endswith("-graph") else args.spec
+                line["reference_gpu_tier"] = BC.ref_cuda_c1(dev, 5, 3, spec)
+            except Exception as e:  # a loader or driver refusal on this machine is a result, not a failure of the bench
+                line["reference_gpu_tier"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         if world == 1 and not args.no_cpu_baseline:
             sec, timed, warmed, kind, what, cores = cpu_timed(1, 1, 45.0)
             line["cpu_baseline"] = {"value": 1.0 / sec, "unit": "img/s", "cores": cores, "kind": kind,
@@ -448,6 +459,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the batched configurations (ViT-g/14, ViT-B/16)")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's own GPU tier (timed last, for context)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

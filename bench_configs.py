@@ -216,6 +216,41 @@ def torch_friendly_c1(dev, steps, warmup):
     return r
 
 
+def ref_cuda_c1(dev, steps, warmup, spec):
+    """The headline workload through the REFERENCE's own GPU tier `spec` (its flash64_* / gemm_tn_* mma.sync kernels,
+    recompiled for this GPU by oracle/make_ref.py: make_kernels, plus cuBLAS for the g0 / g1 GEMMs), from oracle/_ref,
+    with its output checked against this library's for the same spec."""
+    import torch
+    from fastbb_b200 import synthetic
+    from fastbb_b200.models.dinov2 import dinov2
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "fastbb", "vit.py")):
+        return {"config": "c1 through the reference's GPU tier", "spec": spec, "unavailable": "oracle/_ref not built (python oracle/make_ref.py)"}
+    sys.path.insert(0, ref_dir)
+    from fastbb import parse_vit_spec
+    from fastbb.models.dinov2 import DinoV2Params
+    from fastbb.vit import FastViT as RefFastViT
+    params = synthetic.make_params("vitl14", seed=0)
+    x = synthetic.make_image(1, 896, 1344, seed=1).to(dev)
+    layers = [4, 11, 17, 23]
+    graphs = spec.endswith("-graph")
+    attn, gacc = parse_vit_spec(spec[:-6] if graphs else spec)
+    m = DinoV2Params("vitl14")
+    m.load_state_dict(params, strict=True)
+    ref = RefFastViT(m.to(dev), attn=attn, gacc=gacc, dtype=torch.float16, graphs=graphs)
+    fn = lambda: ref.get_intermediate_layers(x, n=layers, return_class_token=True)  # noqa: E731
+    with torch.no_grad():
+        got = fn()
+        torch.cuda.synchronize()
+        ms = timed(fn, dev, steps, warmup)
+        ours = dinov2("vitl14", params, spec=spec[:-6] if graphs else spec, device=dev).get_intermediate_layers(x, n=layers, return_class_token=True)
+    err = max(float((a[0].float() - b[0].float()).norm() / b[0].float().norm()) for a, b in zip(got, ours))
+    r = record("c1 ViT-L/14 896x1344 (6145 tokens) b1, the reference's own GPU tier", spec, 1, 1, 1, ms, stack_flops(6145, 1, 1024, 24), steps)
+    r["what"] = "the reference package (oracle/_ref): its flash64 / gemm_tn kernels recompiled for this GPU, cuBLAS GEMMs for g0 / g1"
+    r["rel_l2_vs_this_library"] = err
+    return r
+
+
 def main():
     import torch
     from fastbb_b200 import replicas
@@ -227,6 +262,7 @@ def main():
     ap.add_argument("--batch", type=int, help="global batch (default: the config's)")
     ap.add_argument("--e2e", action="store_true", help="also time host-to-host through HostPipeline")
     ap.add_argument("--torch", action="store_true", help="only the library-operator line for the headline workload")
+    ap.add_argument("--ref-cuda", metavar="SPEC", help="only the headline workload through the reference's own GPU tier SPEC (e.g. fh-g0, hh-g1-graph)")
     args = ap.parse_args()
     rank, local_rank, world = replicas.init_process_group()
     torch.cuda.set_device(local_rank)
@@ -239,6 +275,9 @@ def main():
     if args.torch:
         if rank == 0:
             emit(torch_friendly_c1(dev, args.steps, args.warmup))
+    elif args.ref_cuda:
+        if rank == 0:
+            emit(ref_cuda_c1(dev, args.steps, args.warmup, args.ref_cuda))
     else:
         if args.only in (None, "c0"):
             emit(run_c0(dev, rank, world, args.steps, args.warmup))

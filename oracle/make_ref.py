@@ -30,6 +30,7 @@ def available():
 def make(src=DEFAULT_SRC, force=False):
     """Returns DEST if the reference is (now) installed there, None if there is no checkout to install from."""
     if available() and not force:
+        make_kernels()
         return DEST
     if not os.path.exists(os.path.join(src, "fastbb", "vit.py")):
         return None
@@ -43,7 +44,32 @@ def make(src=DEFAULT_SRC, force=False):
         ok = subprocess.run(cmd, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL).returncode == 0 and available()
         if not ok:
             shutil.copytree(os.path.join(copy, "fastbb"), os.path.join(DEST, "fastbb"), dirs_exist_ok=True)
+    if available():
+        make_kernels()
     return DEST if available() else None
+
+
+def make_kernels(arch="sm_100"):
+    """Compile the reference's own kernel file for the GPU machine's architecture with the reference's own recipe
+    (fastbb/kernels.py:84-94: `nvcc -cubin -O3 -std=c++17 --expt-relaxed-constexpr -arch=sm_XY`) into
+    oracle/_ref/fastbb/prebuilt/, under the file name its loader looks for (source hash + architecture), so that its GPU
+    tiers (`fh-g0`, `hh-g1`: mma.sync kernels, recompiled) can be timed beside this library's on the same GPU
+    (`bench_configs.py --ref-cuda`) without a compile on that machine. Returns the path, or None without nvcc."""
+    import hashlib
+    src = os.path.join(DEST, "fastbb", "fastbb_kernels.cu")
+    nvcc = shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    if not (os.path.exists(src) and os.path.exists(nvcc)):
+        return None
+    tag = hashlib.sha1(open(src, "rb").read() + arch.encode()).hexdigest()[:16]
+    out = os.path.join(DEST, "fastbb", "prebuilt", f"fastbb_kernels_{tag}.cubin")
+    if not os.path.exists(out):
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        cuda_home = os.path.dirname(os.path.dirname(nvcc))
+        cmd = [nvcc, "-cubin", "-O3", "-std=c++17", "--expt-relaxed-constexpr", f"-arch={arch}", f"-I{cuda_home}/include", "-o", out + ".tmp", src]
+        if subprocess.run(cmd, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL).returncode != 0:
+            return None
+        os.replace(out + ".tmp", out)
+    return out
 
 
 if __name__ == "__main__":
