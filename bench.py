@@ -148,6 +148,50 @@ def workload_config():
             "l2": "no explicit flush: each step streams 604 MB of weights plus ~100 MB activations per block through the 126 MB L2"}
 
 
+def reference_gpu_tiers(steps=5, warmup=3):
+    """For context beside the CPU figure, when this machine has a GPU: the same workload through the reference's own GPU
+    tiers, unmodified, from oracle/_ref - `fh-g0` (its flash64_* mma.sync kernel, recompiled for this architecture by
+    oracle/make_ref.py: make_kernels, cuBLAS GEMMs) and `sdpa-g0` in fp16 (its friendly tier: PyTorch operators). ms per
+    image, CUDA events around `steps` calls. Nothing of this repository's library is on that path."""
+    import torch
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not torch.cuda.is_available():
+        return {"unavailable": "no CUDA device"}
+    if not os.path.exists(os.path.join(ref_dir, "fastbb", "vit.py")):
+        return {"unavailable": "oracle/_ref not built (python oracle/make_ref.py)"}
+    from oracle import vit_oracle as O
+    sys.path.insert(0, ref_dir)
+    from fastbb import parse_vit_spec
+    from fastbb.models.dinov2 import DinoV2Params
+    from fastbb.vit import FastViT as RefFastViT
+    dev = torch.device("cuda", 0)
+    params = O.make_params(ARCH, seed=0)
+    x = O.make_image(1, IMG_H, IMG_W, seed=1).to(dev)
+    out = {"what": "the reference package (oracle/_ref) on cuda:0, fp16: ms per image", "steps": steps}
+    for spec in ("fh-g0", "sdpa-g0"):
+        try:
+            attn, gacc = parse_vit_spec(spec)
+            m = DinoV2Params(ARCH)
+            m.load_state_dict(params, strict=True)
+            ref = RefFastViT(m.to(dev), attn=attn, gacc=gacc, dtype=torch.float16)
+            with torch.no_grad():
+                for _ in range(warmup):
+                    ref.get_intermediate_layers(x, n=LAYERS, return_class_token=True)
+                torch.cuda.synchronize()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(steps):
+                    ref.get_intermediate_layers(x, n=LAYERS, return_class_token=True)
+                e.record()
+                torch.cuda.synchronize()
+            out[spec] = s.elapsed_time(e) / steps
+            del ref, m
+            torch.cuda.empty_cache()
+        except Exception as err:  # a loader or driver refusal on this machine is a result, not a failure of the arm
+            out[spec] = {"unavailable": f"{type(err).__name__}: {err}"[:300]}
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -161,6 +205,8 @@ def run_reference(args, rank, world):
             "config": workload_config(), "arm": what,
             "cpu_baseline": {"value": value, "unit": "img/s", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    if not args.no_reference_gpu:
+        line["gpu_tiers_ms_per_image"] = reference_gpu_tiers()
     print(json.dumps(line), flush=True)
 
 
@@ -432,17 +478,6 @@ def run_ours(args, rank, local_rank, world):
         }
         if configs is not None:
             line["configs"] = configs
-        if world == 1 and not args.no_reference_gpu:
-            # For context, after everything of this library has been timed: the same workload through the reference's own
-            # GPU tier (its mma.sync kernels recompiled for this GPU, from oracle/_ref). Not the reference arm, which is
-            # `--impl reference`.
-            try:
-                import bench_configs as BC
-                torch.cuda.empty_cache()
-                spec = args.spec[:-6] if args.spec.endswith("-graph") else args.spec
-                line["reference_gpu_tier"] = BC.ref_cuda_c1(dev, 5, 3, spec)
-            except Exception as e:  # a loader or driver refusal on this machine is a result, not a failure of the bench
-                line["reference_gpu_tier"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         if world == 1 and not args.no_cpu_baseline:
             sec, timed, warmed, kind, what, cores = cpu_timed(1, 1, 45.0)
             line["cpu_baseline"] = {"value": 1.0 / sec, "unit": "img/s", "cores": cores, "kind": kind,
@@ -459,7 +494,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the batched configurations (ViT-g/14, ViT-B/16)")
-    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's own GPU tier (timed last, for context)")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="reference arm: skip the reference's own GPU tiers (timed after the CPU passes, for context)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

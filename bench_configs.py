@@ -6,9 +6,9 @@ for its batched-split record): images/s, ms per batch and TFLOP/s for
   c2  timm-style ViT-B/16 block stack, 1024x1024 (4097 tokens), batch 1 and 8, install_vit_blocks(..., "fh-g1")
   c3  DINOv2 ViT-g/14 (SwiGLU), 518x518 (1370 tokens), global batch 32, spec hh-g1
   c1-torch  (--torch) the headline workload on the SAME GPU through plain PyTorch operators in fp16 (F.linear, SDPA,
-      F.layer_norm, F.gelu, addcmul): the reference's own friendly tier when its package is present under oracle/_ref
-      (FastViT(attn="sdpa", gacc=False, dtype=float16), fastbb/vit.py:108-150), else the same operator sequence written
-      out here. This is the library bar on this machine: cuBLAS / cuDNN / aten kernels, none of this repository's.
+      F.layer_norm, F.gelu, addcmul), the operator sequence of the reference's friendly tier (fastbb/vit.py:108-150)
+      written out here. This is the library bar on this machine: cuBLAS / cuDNN / aten kernels, none of this
+      repository's. (The reference package itself, CPU and GPU tiers, is timed by `bench.py --impl reference`.)
 
     python bench_configs.py [--only c3] [--steps 20] [--torch]
     python -m torch.distributed.run --nproc-per-node 8 ... bench_configs.py --only c3      # batch sharded 4 per GPU
@@ -179,75 +179,29 @@ def torch_friendly_c1(dev, steps, warmup):
     params = synthetic.make_params("vitl14", seed=0)
     x = synthetic.make_image(1, 896, 1344, seed=1).to(dev)
     layers = [4, 11, 17, 23]
-    ref_dir = os.path.join(ROOT, "oracle", "_ref")
-    if os.path.exists(os.path.join(ref_dir, "fastbb", "vit.py")):
-        sys.path.insert(0, ref_dir)
-        from fastbb.models.dinov2 import DinoV2Params
-        from fastbb.vit import FastViT as RefFastViT
-        m = DinoV2Params("vitl14")
-        m.load_state_dict(params, strict=True)
-        ref = RefFastViT(m.to(dev), attn="sdpa", gacc=False, dtype=torch.float16)
-        fn = lambda: ref.get_intermediate_layers(x, n=layers, return_class_token=True)  # noqa: E731
-        kind = "the reference's friendly tier itself (oracle/_ref), fp16 on this GPU: F.linear, SDPA, nn.LayerNorm, F.gelu, addcmul"
-    else:
-        from fastbb_b200.models.dinov2 import dinov2
-        fast = dinov2("vitl14", params, spec="fh-g0", device=dev)   # only for its tokenizer and module tree
-        vit = fast.vit
+    from fastbb_b200.models.dinov2 import dinov2
+    fast = dinov2("vitl14", params, spec="fh-g0", device=dev)   # only for its tokenizer and module tree
+    vit = fast.vit
 
-        def fn():
-            t = fast.tokens(x)
-            out = []
-            for i, b in enumerate(fast.blocks):
-                B, N, C = t.shape
-                qkv = F.linear(b.norm1(t), b.attn.qkv.weight, b.attn.qkv.bias).view(B, N, 3, 16, 64)
-                q, k, v = (u.transpose(1, 2) for u in qkv.unbind(2))
-                o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, N, C)
-                t = torch.addcmul(t, F.linear(o, b.attn.proj.weight, b.attn.proj.bias), b.ls1.gamma)
-                h = F.gelu(F.linear(b.norm2(t), b.mlp.fc1.weight, b.mlp.fc1.bias))
-                t = t.addcmul(F.linear(h, b.mlp.fc2.weight, b.mlp.fc2.bias), b.ls2.gamma)
-                if i in layers:
-                    out.append(vit.norm(t))
-            return out
-        kind = "plain PyTorch fp16 operators written out (reference package not present): F.linear, SDPA, nn.LayerNorm, F.gelu, addcmul"
+    def fn():
+        t = fast.tokens(x)
+        out = []
+        for i, b in enumerate(fast.blocks):
+            B, N, C = t.shape
+            qkv = F.linear(b.norm1(t), b.attn.qkv.weight, b.attn.qkv.bias).view(B, N, 3, 16, 64)
+            q, k, v = (u.transpose(1, 2) for u in qkv.unbind(2))
+            o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, N, C)
+            t = torch.addcmul(t, F.linear(o, b.attn.proj.weight, b.attn.proj.bias), b.ls1.gamma)
+            h = F.gelu(F.linear(b.norm2(t), b.mlp.fc1.weight, b.mlp.fc1.bias))
+            t = t.addcmul(F.linear(h, b.mlp.fc2.weight, b.mlp.fc2.bias), b.ls2.gamma)
+            if i in layers:
+                out.append(vit.norm(t))
+        return out
+    kind = "plain PyTorch fp16 operators, written out as the reference's friendly tier runs them: F.linear, SDPA, nn.LayerNorm, F.gelu, addcmul"
     with torch.no_grad():
         ms = timed(fn, dev, steps, warmup)
     r = record("c1 ViT-L/14 896x1344 (6145 tokens) b1, library operators", "torch fp16 eager", 1, 1, 1, ms, stack_flops(6145, 1, 1024, 24), steps)
     r["what"] = kind
-    return r
-
-
-def ref_cuda_c1(dev, steps, warmup, spec):
-    """The headline workload through the REFERENCE's own GPU tier `spec` (its flash64_* / gemm_tn_* mma.sync kernels,
-    recompiled for this GPU by oracle/make_ref.py: make_kernels, plus cuBLAS for the g0 / g1 GEMMs), from oracle/_ref,
-    with its output checked against this library's for the same spec."""
-    import torch
-    from fastbb_b200 import synthetic
-    from fastbb_b200.models.dinov2 import dinov2
-    ref_dir = os.path.join(ROOT, "oracle", "_ref")
-    if not os.path.exists(os.path.join(ref_dir, "fastbb", "vit.py")):
-        return {"config": "c1 through the reference's GPU tier", "spec": spec, "unavailable": "oracle/_ref not built (python oracle/make_ref.py)"}
-    sys.path.insert(0, ref_dir)
-    from fastbb import parse_vit_spec
-    from fastbb.models.dinov2 import DinoV2Params
-    from fastbb.vit import FastViT as RefFastViT
-    params = synthetic.make_params("vitl14", seed=0)
-    x = synthetic.make_image(1, 896, 1344, seed=1).to(dev)
-    layers = [4, 11, 17, 23]
-    graphs = spec.endswith("-graph")
-    attn, gacc = parse_vit_spec(spec[:-6] if graphs else spec)
-    m = DinoV2Params("vitl14")
-    m.load_state_dict(params, strict=True)
-    ref = RefFastViT(m.to(dev), attn=attn, gacc=gacc, dtype=torch.float16, graphs=graphs)
-    fn = lambda: ref.get_intermediate_layers(x, n=layers, return_class_token=True)  # noqa: E731
-    with torch.no_grad():
-        got = fn()
-        torch.cuda.synchronize()
-        ms = timed(fn, dev, steps, warmup)
-        ours = dinov2("vitl14", params, spec=spec[:-6] if graphs else spec, device=dev).get_intermediate_layers(x, n=layers, return_class_token=True)
-    err = max(float((a[0].float() - b[0].float()).norm() / b[0].float().norm()) for a, b in zip(got, ours))
-    r = record("c1 ViT-L/14 896x1344 (6145 tokens) b1, the reference's own GPU tier", spec, 1, 1, 1, ms, stack_flops(6145, 1, 1024, 24), steps)
-    r["what"] = "the reference package (oracle/_ref): its flash64 / gemm_tn kernels recompiled for this GPU, cuBLAS GEMMs for g0 / g1"
-    r["rel_l2_vs_this_library"] = err
     return r
 
 
@@ -262,7 +216,6 @@ def main():
     ap.add_argument("--batch", type=int, help="global batch (default: the config's)")
     ap.add_argument("--e2e", action="store_true", help="also time host-to-host through HostPipeline")
     ap.add_argument("--torch", action="store_true", help="only the library-operator line for the headline workload")
-    ap.add_argument("--ref-cuda", metavar="SPEC", help="only the headline workload through the reference's own GPU tier SPEC (e.g. fh-g0, hh-g1-graph)")
     args = ap.parse_args()
     rank, local_rank, world = replicas.init_process_group()
     torch.cuda.set_device(local_rank)
@@ -275,9 +228,6 @@ def main():
     if args.torch:
         if rank == 0:
             emit(torch_friendly_c1(dev, args.steps, args.warmup))
-    elif args.ref_cuda:
-        if rank == 0:
-            emit(ref_cuda_c1(dev, args.steps, args.warmup, args.ref_cuda))
     else:
         if args.only in (None, "c0"):
             emit(run_c0(dev, rank, world, args.steps, args.warmup))

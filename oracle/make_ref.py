@@ -3,8 +3,9 @@
     python oracle/make_ref.py [/path/to/reference]          (default: $FASTBB_REFERENCE, then the build container's checkout)
 
 TEST / BENCH INFRASTRUCTURE ONLY. What lands in oracle/_ref/ is the reference's own, unmodified `fastbb` package; only
-bench.py's CPU legs (`--impl reference`, `cpu_baseline`) and tests may import it, to time and check the reference's
-friendly fp32 tier (FastViT(attn="sdpa", gacc=False, dtype=float32), fastbb/vit.py:42,108-150) on the host cores.
+bench.py's reference legs (`--impl reference`, `cpu_baseline`) and tests may import it: to time and check the reference's
+friendly fp32 tier (FastViT(attn="sdpa", gacc=False, dtype=float32), fastbb/vit.py:42,108-150) on the host cores and,
+in the `--impl reference` arm on a machine with a GPU, to time its own GPU tiers beside that for context.
 Nothing under fastbb_b200/ imports it. The reference checkout itself does not travel to the GPU machine; this folder,
 like the built .so files, does.
 
@@ -53,8 +54,8 @@ def make_kernels(arch="sm_100"):
     """Compile the reference's own kernel file for the GPU machine's architecture with the reference's own recipe
     (fastbb/kernels.py:84-94: `nvcc -cubin -O3 -std=c++17 --expt-relaxed-constexpr -arch=sm_XY`) into
     oracle/_ref/fastbb/prebuilt/, under the file name its loader looks for (source hash + architecture), so that its GPU
-    tiers (`fh-g0`, `hh-g1`: mma.sync kernels, recompiled) can be timed beside this library's on the same GPU
-    (`bench_configs.py --ref-cuda`) without a compile on that machine. Returns the path, or None without nvcc."""
+    tiers (`fh-g0`, `hh-g1`: mma.sync kernels, recompiled) can be timed on the same GPU as this library
+    (`bench.py --impl reference`: gpu_tiers_ms_per_image) without a compile on that machine. Returns the path, or None without nvcc."""
     import hashlib
     src = os.path.join(DEST, "fastbb", "fastbb_kernels.cu")
     nvcc = shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
