@@ -1,6 +1,8 @@
 """The CPU oracle against the reference's own outputs (tests/golden/*.npz, made by tests/golden/make_golden.py by running
 the reference's fp32 tier) and against naive float64 restatements. Tolerances are fp32 round-off: the oracle and the
 reference compute the same formulas with different summation orders."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -171,3 +173,22 @@ def test_linear_epilogue_order_naive():
     assert np.allclose(O.linear(t(x), t(w), t(b), act="swiglu").numpy(), want2, atol=1e-5)
     with pytest.raises(ValueError):
         O.linear(t(x), t(w), act="relu")
+
+
+def test_reference_package_and_its_gpu_kernels_build_into_oracle_ref():
+    """oracle/make_ref.py where a checkout (or an earlier install) of the reference is at hand: the package lands in
+    oracle/_ref and its kernel file compiles for sm_100 under the very file name the reference's loader looks for
+    (sha1 of the source + architecture, fastbb/kernels.py:84-87), so the GPU machine needs no compiler run."""
+    import hashlib
+    import shutil
+    from oracle import make_ref
+    dest = make_ref.make()
+    if dest is None:
+        pytest.skip("no reference checkout and no oracle/_ref here")
+    assert make_ref.available()
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("no nvcc")
+    out = make_ref.make_kernels()
+    src = os.path.join(dest, "fastbb", "fastbb_kernels.cu")
+    tag = hashlib.sha1(open(src, "rb").read() + b"sm_100").hexdigest()[:16]
+    assert out == os.path.join(dest, "fastbb", "prebuilt", f"fastbb_kernels_{tag}.cubin") and os.path.getsize(out) > 100_000
