@@ -47,7 +47,7 @@ NOMINAL_FP16_TFLOPS = 2250.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one flash-attention launch at this workload, from one ncu capture of the
 # kernel (37.86 MB read, 0.64 MB written: the inputs once; the output and the split groups' partial results stay in L2).
 ATTN_DRAM_TRAFFIC_BYTES = 37862912 + 637184
-CPU_SECONDS_BUDGET = 75.0   # the reference arm stops adding timed passes once this much CPU time has been spent
+CPU_SECONDS_LIMIT = 75.0   # the reference arm stops adding timed passes once this much CPU time has been spent
 
 
 def measured_peaks():
@@ -119,9 +119,9 @@ def cpu_forward():
             "CPU restatement of the reference's fp32 tier (oracle/vit_oracle.py); the reference package is not installed under oracle/_ref")
 
 
-def cpu_timed(steps, warmup, budget_s):
+def cpu_timed(steps, warmup, limit_s):
     """Whole forward passes, each actually timed: `warmup` untimed (at most one), then up to `steps`, stopping early once
-    the budget is spent. Returns (seconds per pass, passes timed, passes warmed, kind, what, cores)."""
+    the limit is reached. Returns (seconds per pass, passes timed, passes warmed, kind, what, cores)."""
     import torch
     fn, kind, what = cpu_forward()
     spent = 0.0
@@ -133,7 +133,7 @@ def cpu_timed(steps, warmup, budget_s):
             spent += time.perf_counter() - t0
             warmed = 1
         times = []
-        while len(times) < max(1, steps) and (not times or spent + times[-1] <= budget_s):
+        while len(times) < max(1, steps) and (not times or spent + times[-1] <= limit_s):
             t0 = time.perf_counter()
             fn()
             times.append(time.perf_counter() - t0)
@@ -195,10 +195,10 @@ def reference_gpu_tiers(steps=5, warmup=3):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    sec, timed, warmed, kind, what, cores = cpu_timed(args.steps, min(args.warmup, 1), CPU_SECONDS_BUDGET)
+    sec, timed, warmed, kind, what, cores = cpu_timed(args.steps, min(args.warmup, 1), CPU_SECONDS_LIMIT)
     value = 1.0 / sec
     sample = (f"{timed} whole forward pass(es) of one {IMG_H}x{IMG_W} image, each timed ({warmed} untimed before); the command asked for "
-              f"{args.steps} steps / {args.warmup} warm-up, the CPU arm stops at {CPU_SECONDS_BUDGET:.0f} s of CPU time")
+              f"{args.steps} steps / {args.warmup} warm-up, the CPU arm stops at {CPU_SECONDS_LIMIT:.0f} s of CPU time")
     line = {"impl": "reference", "metric": "images_per_s", "value": value, "unit": "img/s", "n_gpus": args.gpus, "steps": timed,
             "warmup": warmed, "steps_requested": args.steps, "warmup_requested": args.warmup, "ms_per_step": 1e3 * sec,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
