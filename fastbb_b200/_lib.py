@@ -63,6 +63,7 @@ PROTOTYPES = {
     "fbb_linear_layernorm_launches": (_i32, [_i64, _i32, _i32, _i32]),
     "fbb_flash64_f16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_flash64_workspace_bytes": (_i64, [_i32, _i32, _i32]),
+    "fbb_flash64_launches": (_i32, [_i32, _i32, _i32, _i32]),
     "fbb_flash64_f16_ws": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp, _i64, _vp]),
     "fbb_flash64_f16_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32] + [_i64] * 12 + [_f32, _i32, _vp]),
     "fbb_stack_scratch_bytes": (_i64, [_bdp, _i32, _i64]),
@@ -92,7 +93,7 @@ def launched(n=1):
 # what libfastbb_flash64.so exports (the other prototypes are skipped when that library is the one loaded)
 FLASH_ONLY_SYMBOLS = ("fbb_version", "fbb_status_string", "fbb_last_error", "fbb_device_status", "fbb_diag_wait_timeout",
                       "fbb_diag_sm_clock_mhz", "fbb_flash64_f16",
-                      "fbb_flash64_workspace_bytes", "fbb_flash64_f16_ws", "fbb_flash64_f16_static")
+                      "fbb_flash64_workspace_bytes", "fbb_flash64_launches", "fbb_flash64_f16_ws", "fbb_flash64_f16_static")
 
 
 def load(path=None):

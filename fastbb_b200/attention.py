@@ -148,7 +148,7 @@ def attention(q, k, v, scale=None, out=None, variant="hh", rows=None, workspace=
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
             float(scale), _lib.FLASH_VARIANT[variant], ws_ptr, ws_bytes, _lib.stream_ptr(q.device)))
-    _lib.launched()
+        _lib.launched(lib.fbb_flash64_launches(B, N, H, int(ws_ptr is not None)))
     return out
 
 

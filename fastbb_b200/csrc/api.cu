@@ -273,6 +273,7 @@ int fbb_linear_layernorm_f16(const void* A, const void* W, void* C, const void* 
 #endif  // FBB_FLASH_ONLY
 
 int64_t fbb_flash64_workspace_bytes(int B, int N, int H) { return flash64_workspace_bytes_for(B, N, H); }
+int fbb_flash64_launches(int B, int N, int H, int has_workspace) { return flash64_launches(B, N, H, has_workspace != 0); }
 
 // Host-side checks shared by the three attention entry points; FBB_OK means the launch may go ahead.
 static int check_flash_args(const void* q, const void* k, const void* v, void* o, int B, int N, int H, const int64_t* qs, const int64_t* ks,

@@ -108,14 +108,26 @@ constexpr int kSlotWarps = 16;
 constexpr int kSlotValues = 36;
 constexpr size_t kSlotFloats = (size_t)kSlotWarps * kSlotValues * 32;
 constexpr size_t kFlagBytesPerCta = kSlotWarps * sizeof(unsigned);
-constexpr size_t flag_region_bytes(int ctas) { return ((size_t)ctas * kFlagBytesPerCta + 255) & ~(size_t)255; }
+// Leftover query rows: every ViT token count is a multiple of the 256-row tile group plus the cls token (and a few
+// registers), and a 25th group per head for ONE row costs the N = 6145 launch 3.5 % (N = 6144: 189 us, 6145: 200 us).
+// Up to kSideMaxRows rows beyond the last full group are therefore not tiled: a second, small launch
+// (flash64_side_rows_kernel) computes them on the CUDA cores. It is the tiled launch's programmatic dependent, so its
+// CTAs (128 threads, 32 registers, no shared memory: what the tiled kernel leaves free on an SM) run beside the tiled
+// kernel's, and it waits for that kernel only at its very end, so that whatever depends on it depends on both.
+constexpr int kSideMaxRows = 8;
+constexpr int kSideMaxChunks = 64;
+constexpr int kSideValues = 66;  // per (row, key chunk): 64 outputs, maximum, sum
+constexpr int kSideMaxTasks = 1024;
+// flag words of the split form, then one counter per leftover row
+constexpr size_t flag_region_bytes(int ctas) { return ((size_t)ctas * (kFlagBytesPerCta + sizeof(unsigned)) + 255) & ~(size_t)255; }
+constexpr size_t side_region_bytes() { return ((size_t)kSideMaxTasks * kSideValues * sizeof(float) + 255) & ~(size_t)255; }
 int64_t flash64_workspace_bytes();
 static bool split_pays(int64_t groups, int sms);
 
 // Built-in workspace of fbb_flash64_f16_static: room for the split form on a device of up to kStaticMaxSms SMs
 // (11.3 MiB; zero-initialised when the module is loaded, as the flag words must be).
 constexpr int kStaticMaxSms = 160;
-constexpr size_t kStaticWsBytes = flag_region_bytes(kStaticMaxSms) + (size_t)kStaticMaxSms * kSlotFloats * sizeof(float);
+constexpr size_t kStaticWsBytes = flag_region_bytes(kStaticMaxSms) + (size_t)kStaticMaxSms * kSlotFloats * sizeof(float) + side_region_bytes();
 static __device__ __align__(256) unsigned char g_flash_static_ws[kStaticWsBytes];
 
 #ifdef FBB_FLASH_TRACE
@@ -142,6 +154,17 @@ struct FlashArgs {
     long long tail_units;    // (groups - rounds * gridDim.x) * nkb, dealt out in equal contiguous shares
     unsigned* ws_flags;      // [gridDim.x][16], all zero between launches; null when no group is ever split
     float* ws_data;          // [gridDim.x][kSlotFloats]
+    int Nq;                  // query rows covered by tiles; rows [Nq, N) are left to flash64_side_rows_kernel
+};
+
+struct SideArgs {
+    const __half *q, *k, *v;
+    __half* o;
+    int64_t q_sb, q_sn, q_sh, k_sb, k_sn, k_sh, v_sb, v_sn, v_sh, o_sb, o_sn, o_sh;
+    int N, H, row0, rows, chunks, tasks;  // rows [row0, row0 + rows) of every (batch, head); tasks = B * H * rows * chunks
+    float scale_log2;
+    unsigned* count;         // [B * H * rows], all zero between launches
+    float* part;             // [tasks][kSideValues]
 };
 
 // A CTA's work is a list of items (group w, key blocks [kb0, kb1)): first `rounds` whole groups taken round-robin
@@ -185,6 +208,109 @@ __device__ __forceinline__ bool wait_slot_flag(const unsigned* flag, int lane, v
     __syncwarp();
     if (ok) (void)ld_acquire_gpu(flag);  // every lane orders its own reads of the slot after the flag
     return ok;
+}
+
+// One warp per (leftover query row, chunk of the keys). Scores: lane j takes key j of each 32-key step (fp32 dot product
+// over the 64 dimensions); then the lanes switch to two output dimensions each and add p_j * v_j for the step's keys, p_j
+// broadcast by shuffle: an online softmax in the scaled log2 domain of the tiled path (x = s * scale_log2). The partial
+// (64 outputs, maximum, sum) goes to the workspace; the warp whose counter update completes a row merges its chunks and
+// stores the row. No warp waits for another. 32 registers (16 CTAs of 128 threads would fit an SM): the point is to fit
+// beside a resident CTA of the tiled kernel, which leaves 4096 registers and no shared memory to spare.
+__global__ void __launch_bounds__(128, 16) flash64_side_rows_kernel(const SideArgs a) {
+    grid_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int task = (int)blockIdx.x * 4 + (int)(threadIdx.x >> 5);
+    if (task < a.tasks) {
+        const int chunk = task % a.chunks, rid = task / a.chunks;
+        const int bh = rid / a.rows;
+        const int row = a.row0 + (rid - bh * a.rows);
+        const int b = bh / a.H, h = bh - b * a.H;
+        const int per = (a.N + a.chunks - 1) / a.chunks;
+        const int k0 = chunk * per, k1 = min(a.N, k0 + per);
+        const uint4* qv = reinterpret_cast<const uint4*>(a.q + b * a.q_sb + (int64_t)row * a.q_sn + h * a.q_sh);
+        const __half* kb = a.k + b * a.k_sb + h * a.k_sh;
+        const __half* vb = a.v + b * a.v_sb + h * a.v_sh + 2 * lane;
+        float m = -INFINITY, l = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll 1
+        for (int j0 = k0; j0 < k1; j0 += 32) {
+            const int j = j0 + lane;
+            float sc = -INFINITY;
+            if (j < k1) {
+                const uint4* kv = reinterpret_cast<const uint4*>(kb + (int64_t)j * a.k_sn);
+                float acc = 0.f;
+#pragma unroll 2
+                for (int d = 0; d < 8; ++d) {
+                    const uint4 kk = __ldcg(kv + d), qq = __ldg(qv + d);  // K and V stream past L1, which holds the tiled kernel's spills
+                    const __half2* kh = reinterpret_cast<const __half2*>(&kk);
+                    const __half2* qh = reinterpret_cast<const __half2*>(&qq);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 kf = __half22float2(kh[e]), qf = __half22float2(qh[e]);
+                        acc = fmaf(kf.x, qf.x, acc);
+                        acc = fmaf(kf.y, qf.y, acc);
+                    }
+                }
+                sc = acc * a.scale_log2;
+            }
+            float mx = sc;
+#pragma unroll
+            for (int sft = 16; sft > 0; sft >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sft));
+            const float mn = fmaxf(m, mx);       // finite: the step holds at least one key
+            const float c = ex2_approx(m - mn);   // 0 on the first step (m = -inf)
+            const float p = ex2_approx(sc - mn);  // 0 for lanes beyond the chunk
+            float ps = p;
+#pragma unroll
+            for (int sft = 16; sft > 0; sft >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, sft);
+            l = l * c + ps;
+            o0 *= c;
+            o1 *= c;
+            m = mn;
+            const int cnt = min(32, k1 - j0);
+#pragma unroll 4
+            for (int jj = 0; jj < cnt; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const unsigned vw = __ldcg(reinterpret_cast<const unsigned*>(vb + (int64_t)(j0 + jj) * a.v_sn));
+                const float2 vf = __half22float2(*reinterpret_cast<const __half2*>(&vw));
+                o0 = fmaf(pj, vf.x, o0);
+                o1 = fmaf(pj, vf.y, o1);
+            }
+        }
+        float* part = a.part + (size_t)task * kSideValues;
+        *reinterpret_cast<float2*>(part + 2 * lane) = make_float2(o0, o1);
+        if (lane == 0) {
+            part[64] = m;
+            part[65] = l;
+        }
+        __threadfence();
+        __syncwarp();
+        unsigned prev = 0u;
+        if (lane == 0) prev = atomicAdd(a.count + rid, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev + 1u == (unsigned)a.chunks) {
+            // this warp completed the row: merge the chunks (an empty chunk has m = -inf and contributes nothing)
+            __threadfence();
+            const float* parts = a.part + (size_t)rid * a.chunks * kSideValues;
+            float M = -INFINITY;
+            for (int ci = 0; ci < a.chunks; ++ci) M = fmaxf(M, __ldcg(parts + ci * kSideValues + 64));
+            float L = 0.f, O0 = 0.f, O1 = 0.f;
+            for (int ci = 0; ci < a.chunks; ++ci) {
+                const float* pc = parts + ci * kSideValues;
+                const float w = ex2_approx(__ldcg(pc + 64) - M);
+                const float2 oc = __ldcg(reinterpret_cast<const float2*>(pc + 2 * lane));
+                L = fmaf(__ldcg(pc + 65), w, L);
+                O0 = fmaf(oc.x, w, O0);
+                O1 = fmaf(oc.y, w, O1);
+            }
+            const float inv = 1.f / L;
+            __half* dst = a.o + b * a.o_sb + (int64_t)row * a.o_sn + h * a.o_sh + 2 * lane;
+            *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(O0 * inv, O1 * inv);
+            if (lane == 0) a.count[rid] = 0u;  // free for the next launch
+        }
+    }
+    // The tiled launch before this one in the stream is still running. Nothing above depends on it (q, k and v were complete
+    // before it started, and the rows written here are not its rows), but whoever waits for THIS grid must find that one
+    // complete as well.
+    grid_dependency_wait();
 }
 
 template <int NQ>
@@ -439,7 +565,7 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 item_at(it, w, kb0, kb1);
                 n = kb1 - kb0;
                 to_end = kb1 == nkb;
-                warp_has_rows = (w % a.groups_per_head) * (FQ * NQ) + t * FQ + lane_base < a.N;
+                warp_has_rows = (w % a.groups_per_head) * (FQ * NQ) + t * FQ + lane_base < a.Nq;
             }
             lA = lB = 0.f;
             bool first = true;
@@ -619,9 +745,9 @@ flash64_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             __half* dstB = dstA + 8 * a.o_sn;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                if (rowA < a.N)
+                if (rowA < a.Nq)
                     *reinterpret_cast<uint32_t*>(dstA + 8 * k) = pack_h2(__uint_as_float(o[4 * k]) * invA, __uint_as_float(o[4 * k + 1]) * invA);
-                if (rowA + 8 < a.N)
+                if (rowA + 8 < a.Nq)
                     *reinterpret_cast<uint32_t*>(dstB + 8 * k) = pack_h2(__uint_as_float(o[4 * k + 2]) * invB, __uint_as_float(o[4 * k + 3]) * invB);
             }
         }
@@ -648,7 +774,7 @@ static int launch_flash_variant(const CUtensorMap& tq, const CUtensorMap& tk, co
         if (e != cudaSuccess) return fail((int)e, "cudaFuncSetAttribute(flash64_umma_kernel): %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
-    a.groups_per_head = (a.N + FQ * NQ - 1) / (FQ * NQ);
+    a.groups_per_head = (a.Nq + FQ * NQ - 1) / (FQ * NQ);
     a.nkb = (a.N + FK - 1) / FK;
     const int64_t groups = (int64_t)a.groups_per_head * B * a.H;
     if (groups > 0x7FFFFFFFll) return fail(FBB_ERR_SHAPE, "flash64: too many query tiles (%lld)", (long long)groups);
@@ -700,14 +826,69 @@ static bool split_pays(int64_t groups, int sms) {
 // Two query tiles per CTA once that still gives every SM a CTA; small inputs take one tile per CTA (the small-token path).
 static bool two_tiles_per_cta(int B, int N, int H) { return (int64_t)((N + 2 * FQ - 1) / (2 * FQ)) * B * H >= num_sms(); }
 
-int64_t flash64_workspace_bytes() { return (int64_t)(flag_region_bytes(num_sms()) + (size_t)num_sms() * kSlotFloats * sizeof(float)); }
+int64_t flash64_workspace_bytes() {
+    return (int64_t)(flag_region_bytes(num_sms()) + (size_t)num_sms() * kSlotFloats * sizeof(float) + side_region_bytes());
+}
+
+// Query rows beyond the last full two-tile group that the side launch takes instead of a tile group of their own
+// (0: none): a few rows (cls token, registers), at most one per SM over all (batch, head) pairs, and the rest still
+// worth two tiles per CTA. FBB_FLASH_NO_SIDE switches it off (tuning and test aid).
+static int side_rows_for(int B, int N, int H) {
+    const int r = N % (2 * FQ);
+    if (r < 1 || r > kSideMaxRows || N <= 2 * FQ || getenv("FBB_FLASH_NO_SIDE") != nullptr || getenv("FBB_FLASH_NO_SPLIT") != nullptr) return 0;
+    const int sms = num_sms();
+    if ((int64_t)B * H * r > sms || !two_tiles_per_cta(B, N - r, H)) return 0;
+    // Only where the tiled launch stays in a persistent form (split, or whole groups in equal rounds). One CTA per group
+    // measured 3 % slower per group than the persistent forms at N = 16385, where dropping the 65th group per head would
+    // have moved the launch from the split form (1040 groups) to one CTA per group (1024): 1453 against 1430 us.
+    const int64_t groups = (int64_t)((N - r) / (2 * FQ)) * B * H;
+    if (!(split_pays(groups, sms) || (groups > sms && groups % sms == 0))) return 0;
+    return r;
+}
 
 int64_t flash64_workspace_bytes_for(int B, int N, int H) {
     if (B <= 0 || N <= 0 || H <= 0 || getenv("FBB_FLASH_NO_SPLIT") != nullptr) return 0;
-    const int nq = two_tiles_per_cta(B, N, H) ? 2 : 1;
-    const int64_t groups = (int64_t)((N + FQ * nq - 1) / (FQ * nq)) * B * H;
+    const int r = side_rows_for(B, N, H);
+    const int nq = two_tiles_per_cta(B, N - r, H) ? 2 : 1;
+    const int64_t groups = (int64_t)((N - r + FQ * nq - 1) / (FQ * nq)) * B * H;
     const int sms = num_sms();
-    return split_pays(groups, sms) ? flash64_workspace_bytes() : 0;
+    return (r > 0 || split_pays(groups, sms)) ? flash64_workspace_bytes() : 0;
+}
+
+int flash64_launches(int B, int N, int H, bool has_workspace) { return (B > 0 && N > 0 && H > 0 && has_workspace && side_rows_for(B, N, H) > 0) ? 2 : 1; }
+
+// The leftover rows [N - rows, N): enqueued right after the tiled launch (see kSideMaxRows).
+static int launch_side_rows(const FlashArgs& f, const void* q, const void* k, const void* v, int B, const int64_t* qs, const int64_t* ks,
+                            const int64_t* vs, int rows, void* ws, cudaStream_t stream) {
+    SideArgs a = {};
+    a.q = reinterpret_cast<const __half*>(q);
+    a.k = reinterpret_cast<const __half*>(k);
+    a.v = reinterpret_cast<const __half*>(v);
+    a.o = f.o;
+    a.q_sb = qs[0]; a.q_sn = qs[1]; a.q_sh = qs[2];
+    a.k_sb = ks[0]; a.k_sn = ks[1]; a.k_sh = ks[2];
+    a.v_sb = vs[0]; a.v_sn = vs[1]; a.v_sh = vs[2];
+    a.o_sb = f.o_sb; a.o_sn = f.o_sn; a.o_sh = f.o_sh;
+    a.N = f.N;
+    a.H = f.H;
+    a.row0 = f.N - rows;
+    a.rows = rows;
+    a.scale_log2 = f.scale_log2;
+    const int sms = num_sms();
+    const int64_t nrows = (int64_t)B * f.H * rows;  // <= sms
+    int64_t chunks = (4 * (int64_t)sms) / nrows;     // about four warps per SM
+    const int64_t most = (f.N + 63) / 64;            // at least two 32-key steps per chunk
+    chunks = chunks > most ? most : chunks;
+    chunks = chunks > kSideMaxChunks ? kSideMaxChunks : (chunks < 1 ? 1 : chunks);
+    while (nrows * chunks > kSideMaxTasks) --chunks;
+    a.chunks = (int)chunks;
+    a.tasks = (int)(nrows * chunks);
+    uint8_t* w8 = reinterpret_cast<uint8_t*>(ws);
+    a.count = reinterpret_cast<unsigned*>(w8 + (size_t)sms * kFlagBytesPerCta);
+    a.part = reinterpret_cast<float*>(w8 + flag_region_bytes(sms) + (size_t)sms * kSlotFloats * sizeof(float));
+    cudaError_t e = launch_pdl(flash64_side_rows_kernel, dim3((unsigned)((a.tasks + 3) / 4)), dim3(128), 0, stream, a);
+    if (e != cudaSuccess) return fail((int)e, "flash64_side_rows_kernel launch: %s", cudaGetErrorString(e));
+    return FBB_OK;
 }
 
 // Address and size of the built-in workspace on the current device; the address is looked up once per device. Enqueues
@@ -761,8 +942,16 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
     a.o_sh = os[2];
     a.scale_log2 = scale * 1.4426950408889634f;
     (void)variant;  // ff, fh and hh run the same kernel on this part (see the note on variants at the top of the file)
-    if (two_tiles_per_cta(B, N, H)) return launch_flash_variant<2>(tq, tk, tv, a, B, ws, ws_bytes, stream);
-    return launch_flash_variant<1>(tq, tk, tv, a, B, ws, ws_bytes, stream);
+    // leftover rows go to the side launch only when the caller lent a workspace (their partial results live there)
+    const int side = ws != nullptr ? side_rows_for(B, N, H) : 0;
+    if (side > 0 && ws_bytes < flash64_workspace_bytes())
+        return fail(FBB_ERR_SHAPE, "flash64: workspace of %lld bytes, %lld needed", (long long)ws_bytes, (long long)flash64_workspace_bytes());
+    a.Nq = N - side;
+    int rc;
+    if (two_tiles_per_cta(B, a.Nq, H)) rc = launch_flash_variant<2>(tq, tk, tv, a, B, ws, ws_bytes, stream);
+    else rc = launch_flash_variant<1>(tq, tk, tv, a, B, ws, ws_bytes, stream);  // (never with side rows: see side_rows_for)
+    if (rc != FBB_OK || side == 0) return rc;
+    return launch_side_rows(a, q, k, v, B, qs, ks, vs, side, ws, stream);
 }
 
 }  // namespace fbb

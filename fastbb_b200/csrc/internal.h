@@ -92,6 +92,7 @@ int launch_flash64(const void* q, const void* k, const void* v, void* o, int B, 
 int flash64_static_workspace(void** ptr, int64_t* bytes, cudaStream_t stream);
 // Workspace the split form needs on the current device for this shape; 0 when the shape is never split.
 int64_t flash64_workspace_bytes_for(int B, int N, int H);
+int flash64_launches(int B, int N, int H, bool has_workspace);
 
 // One FFI crossing per block / stack (block.cu): scratch needed for `tokens` tokens, and the launches themselves.
 int64_t stack_scratch_bytes(const fbb_block_desc* d, int n_blocks, int64_t tokens);

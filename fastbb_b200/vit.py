@@ -254,7 +254,9 @@ def run_stack(blocks, x, attn_variant, gacc):
         _lib.check(lib.fbb_stack_forward_f16(descs, n, x.data_ptr(), B, N, scratch.data_ptr(), scratch.numel(),
                                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                                              _lib.stream_ptr(x.device)))
-    _lib.launched(lib.fbb_stack_launches(descs, n, B * N))
+    with _lib.on(x.device):  # (the attention launch count depends on the device's SM count)
+        flash = lib.fbb_flash64_launches(B, N, descs[0].heads, int(ws is not None))
+    _lib.launched(lib.fbb_stack_launches(descs, n, B * N) + n * (flash - 1))
     return True
 
 

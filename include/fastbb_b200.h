@@ -155,13 +155,19 @@ int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B,
  * split over two CTAs is merged through the workspace (unnormalised fp32 partial results + running maxima / sums).
  * No counterpart in the reference (its kernels run one CTA per query tile); results are the same up to fp32 rounding
  * of the merge.
- *   fbb_flash64_workspace_bytes(B, N, H): bytes needed on the current device for this shape, 0 if it is never split.
+ * With a workspace the few query rows beyond the last full 256-row tile group (the cls token and registers of a ViT: at
+ * most 8 rows, at most one per SM over all batch x head pairs) are not tiled either: a second, small launch computes
+ * them on the CUDA cores beside the tiled one (partial results per key chunk in the workspace, merged by the warp that
+ * completes a row), so that one row does not cost every head a tile group.
+ *   fbb_flash64_workspace_bytes(B, N, H): bytes needed on the current device for this shape, 0 if it uses none.
+ *   fbb_flash64_launches(B, N, H, has_workspace): kernel launches the call enqueues (1, or 2 with leftover rows).
  *   workspace: device memory of at least that size, 16-byte aligned, ZEROED once by the caller before its first use;
- *     it starts with one flag word per softmax warp and SM (64 bytes per SM), which every launch leaves zero again, so
- *     it can be reused by any later call of any shape; the rest is overwritten freely. null (or a shape that needs
+ *     it starts with one flag word per softmax warp and SM and one counter per SM (68 bytes per SM), which every launch
+ *     leaves zero again, so it can be reused by any later call of any shape; the rest is overwritten freely. null (or a shape that needs
  *     none) gives exactly fbb_flash64_f16. Calls that may overlap in time (different streams) need different workspaces.
  *     If fbb_device_status() ever reports a failed wait, zero the workspace again before reusing it. */
 int64_t fbb_flash64_workspace_bytes(int B, int N, int H);
+int fbb_flash64_launches(int B, int N, int H, int has_workspace);
 int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int B, int N, int H, int64_t q_sb, int64_t q_sn,
                        int64_t q_sh, int64_t k_sb, int64_t k_sn, int64_t k_sh, int64_t v_sb, int64_t v_sn, int64_t v_sh,
                        int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace,
