@@ -5,7 +5,7 @@
 // ones the per-operator entry points launch, so the results are bit-identical to calling those one by one.
 // Each residual GEMM is followed by a LayerNorm of its output (proj by norm2 of the same block, fc2 by norm1 of the next
 // block of the run): those pairs go through launch_linear_layernorm, which fuses them into one launch where the shape
-// allows, so a block of the run costs five to seven launches. Only the first block of a run normalises its own input.
+// allows, so a block of the run costs five to seven launches (one more where the attention adds its side launch for leftover rows). Only the first block of a run normalises its own input.
 #include "internal.h"
 
 namespace fbb {

@@ -9,7 +9,8 @@ graphs per input shape. What differs is below the operator calls: one block is
     LayerNorm kernel -> qkv GEMM (+bias) -> flash attention -> proj GEMM (+bias, LayerScale, residual)
     LayerNorm kernel -> fc1 GEMM (+bias, GELU) | w12 GEMM (+bias, SwiGLU) -> fc2 | w3 GEMM (+bias, LayerScale, residual)
 
-seven launches of this package's own sm_100a kernels, with no torch fallback for small inputs or unsupported layouts
+seven launches of this package's own sm_100a kernels (eight where the attention hands the cls / register rows to its side
+launch), with no torch fallback for small inputs or unsupported layouts
 (the reference switches to SDPA below 2.2e5 elements, fastbb/vit.py:37,146; here the attention kernel has its own
 small-input configuration). The process-global cuBLAS fp16-accumulation flag the reference flips around a run
 (fastbb/vit.py:27-34) is never touched: the accumulate mode is an argument of each GEMM.
@@ -232,7 +233,7 @@ _DESCS = weakref.WeakKeyDictionary()  # block module -> _CachedDesc (kept outsid
 
 def run_stack(blocks, x, attn_variant, gacc):
     """blocks[...] applied IN PLACE to x [B, N, C] (fp16, contiguous, CUDA) through ONE call of the C stack runner
-    (fbb_stack_forward_f16: 7 launches per block, the same kernels in the same order as run_block). Returns False
+    (fbb_stack_forward_f16: 7 or 8 launches per block, the same kernels in the same order as run_block). Returns False
     without touching x if some block is outside what the runner covers; the caller then uses run_block."""
     n = len(blocks)
     descs = (_lib.BlockDesc * n)()
