@@ -831,13 +831,17 @@ int64_t flash64_workspace_bytes() {
 }
 
 // Query rows beyond the last full two-tile group that the side launch takes instead of a tile group of their own
-// (0: none): a few rows (cls token, registers), at most one per SM over all (batch, head) pairs, and the rest still
-// worth two tiles per CTA. FBB_FLASH_NO_SIDE switches it off (tuning and test aid).
+// (0: none): a few rows (cls token, registers), few enough in all and a sequence long enough for the side launch to
+// hide behind the tiled one, and the rest still worth two tiles per CTA. FBB_FLASH_NO_SIDE switches it off (tuning and test aid).
 static int side_rows_for(int B, int N, int H) {
     const int r = N % (2 * FQ);
     if (r < 1 || r > kSideMaxRows || N <= 2 * FQ || getenv("FBB_FLASH_NO_SIDE") != nullptr || getenv("FBB_FLASH_NO_SPLIT") != nullptr) return 0;
     const int sms = num_sms();
-    if ((int64_t)B * H * r > sms || !two_tiles_per_cta(B, N - r, H)) return 0;
+    // The side launch gets four warps per SM (what fits beside the tiled kernel) and each of them is bound by the latency
+    // of its loads, so it only hides behind the tiled launch when that is long and the rows are few. Measured on B200
+    // (side / tiled only, us): N = 6145, 16 rows 194 / 200; 4097, 12 rows 76.1 / 77.5; 3073, 16 rows 61.5 / 62.6; 2561
+    // 47.8 / 47.4; but 6149 (5 rows per head: 80 rows) 308 / 200 and 1281 with 64 rows 63.6 / 55.5.
+    if ((int64_t)B * H * r > sms / 8 || N < 3072 || !two_tiles_per_cta(B, N - r, H)) return 0;
     // Only where the tiled launch stays in a persistent form (split, or whole groups in equal rounds). One CTA per group
     // measured 3 % slower per group than the persistent forms at N = 16385, where dropping the 65th group per head would
     // have moved the launch from the split form (1040 groups) to one CTA per group (1024): 1453 against 1430 us.

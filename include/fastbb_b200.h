@@ -156,7 +156,7 @@ int fbb_flash64_f16(const void* q, const void* k, const void* v, void* o, int B,
  * No counterpart in the reference (its kernels run one CTA per query tile); results are the same up to fp32 rounding
  * of the merge.
  * With a workspace the few query rows beyond the last full 256-row tile group (the cls token and registers of a ViT: at
- * most 8 rows, at most one per SM over all batch x head pairs) are not tiled either: a second, small launch computes
+ * most 8 rows per head and 18 over all batch x head pairs, sequences of 3072 tokens and more) are not tiled either: a second, small launch computes
  * them on the CUDA cores beside the tiled one (partial results per key chunk in the workspace, merged by the warp that
  * completes a row), so that one row does not cost every head a tile group.
  *   fbb_flash64_workspace_bytes(B, N, H): bytes needed on the current device for this shape, 0 if it uses none.

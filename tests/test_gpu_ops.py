@@ -528,12 +528,13 @@ def test_flash_split_form_matches_one_cta_per_group(oracle, variant, B, N, H):
     status_ok()
 
 
-@pytest.mark.parametrize("B,N,H,side", [(1, 2561, 16, True), (1, 2565, 16, True), (1, 2568, 16, True), (1, 2569, 16, False),
-                                         (2, 1281, 32, True), (10, 513, 16, False), (1, 6149, 16, True), (1, 2049, 16, False)])
+@pytest.mark.parametrize("B,N,H,side", [(1, 6145, 16, True), (1, 4097, 12, True), (1, 3329, 16, True), (1, 6146, 8, True),
+                                         (1, 32776, 2, True), (1, 2561, 16, False), (1, 6149, 16, False), (1, 6153, 16, False),
+                                         (10, 513, 16, False), (2, 1281, 32, False)])
 def test_flash_leftover_rows_by_the_side_launch(oracle, B, N, H, side):
     """A few query rows beyond the last full 256-row group (cls token, registers) are computed by a second, small launch
-    on the CUDA cores instead of a tile group per head - when a workspace is lent, they are at most 8 per head and one
-    per SM in all, and the rest still fills the SMs with two-tile CTAs. Those rows must match the oracle and the tiled
+    on the CUDA cores instead of a tile group per head - when a workspace is lent, they are at most 8 per head and 18
+    in all, the sequence has at least 3072 tokens, and the rest still fills the SMs with two-tile CTAs in a persistent form. Those rows must match the oracle and the tiled
     path, every other row must be what the tiled path gives, and the row counters must be zero again afterwards."""
     from fastbb_b200 import _lib
     from fastbb_b200.attention import attention
