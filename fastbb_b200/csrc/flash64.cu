@@ -820,7 +820,9 @@ extern "C" int fbb_flash_trace_buffer(void* buf) {
 static bool split_pays(int64_t groups, int sms) {
     if (groups <= sms || groups % sms == 0) return false;
     const int64_t whole = (groups + sms - 1) / sms;
-    return (double)(whole * sms - groups) >= 0.09 * (double)(whole * sms);
+    const char* f = getenv("FBB_FLASH_SPLIT_WASTE");  // tuning aid: the least wasted share of the whole-wave schedule that splits
+    const double least = f != nullptr ? atof(f) : 0.09;
+    return (double)(whole * sms - groups) >= least * (double)(whole * sms);
 }
 
 // Two query tiles per CTA once that still gives every SM a CTA; small inputs take one tile per CTA (the small-token path).
