@@ -125,7 +125,7 @@ int64_t flash64_workspace_bytes();
 static bool split_pays(int64_t groups, int sms);
 
 // Built-in workspace of fbb_flash64_f16_static: room for the split form on a device of up to kStaticMaxSms SMs
-// (11.3 MiB; zero-initialised when the module is loaded, as the flag words must be).
+// (11.5 MiB; zero-initialised when the module is loaded, as the flag words must be).
 constexpr int kStaticMaxSms = 160;
 constexpr size_t kStaticWsBytes = flag_region_bytes(kStaticMaxSms) + (size_t)kStaticMaxSms * kSlotFloats * sizeof(float) + side_region_bytes();
 static __device__ __align__(256) unsigned char g_flash_static_ws[kStaticWsBytes];

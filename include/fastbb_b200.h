@@ -173,7 +173,7 @@ int fbb_flash64_f16_ws(const void* q, const void* k, const void* v, void* o, int
                        int64_t o_sb, int64_t o_sn, int64_t o_sh, float scale, int variant, void* workspace,
                        int64_t workspace_bytes, void* stream);
 
-/* fbb_flash64_f16_ws with the workspace built into the library: a file-scope device array of 11.3 MiB, enough for the
+/* fbb_flash64_f16_ws with the workspace built into the library: a file-scope device array of 11.5 MiB, enough for the
  * split form on devices of up to 160 SMs (a device that needs more is rejected with FBB_ERR_SHAPE; shapes that are never
  * split do not touch it). No counterpart in the reference. The call allocates and frees nothing: the array's address
  * is looked up once per device (cudaGetSymbolAddress, with that device current) and kept.
