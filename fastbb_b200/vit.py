@@ -188,7 +188,8 @@ class _CachedDesc:
     still describes the block: the submodules and parameter tensors (by identity and device address) and the plain
     attributes that went into it. Reading a block afresh costs ~20 us of Python (module attribute lookups); at ViT-S
     sizes that was a third of an eager forward pass."""
-    __slots__ = ("desc", "mods", "params", "attrs", "cfg")
+    __slots__ = ("desc", "mods", "params", "attrs", "cfg", "serial")
+    _count = 0
 
     @staticmethod
     def _attrs(block):
@@ -200,18 +201,22 @@ class _CachedDesc:
         _fill_block_desc(self.desc, block, attn_variant, gacc)
         self.cfg = (attn_variant, gacc)
         a, m = block.attn, block.mlp
-        leaves = [(block, n) for n in ("norm1", "norm2", "ls1", "ls2")] + [(a, "qkv"), (a, "proj")]
+        # (parent, name, child) with parent None standing for the block itself: this object is the value of a weak-keyed
+        # table whose key is the block, so it must not hold the block (its submodules do not point back to it)
+        leaves = [(None, n) for n in ("norm1", "norm2", "ls1", "ls2")] + [(a, "qkv"), (a, "proj")]
         leaves += [(m, n) for n in (("fc1", "fc2", "act") if hasattr(m, "fc1") else ("w12", "w3"))]
-        self.mods = [(block, "attn", a), (block, "mlp", m)] + [(parent, n, parent._modules.get(n)) for parent, n in leaves]
+        self.mods = [(None, "attn", a), (None, "mlp", m)] + [(parent, n, (block if parent is None else parent)._modules.get(n)) for parent, n in leaves]
         self.params = [(leaf, n, t, None if t is None else t.data_ptr())
                        for _, _, leaf in self.mods[2:] if leaf is not None for n, t in leaf._parameters.items()]
         self.attrs = self._attrs(block)
+        _CachedDesc._count += 1
+        self.serial = _CachedDesc._count  # names this reading of the block in other tables without keeping it alive
 
     def valid(self, block, attn_variant, gacc):
         if self.cfg != (attn_variant, gacc):
             return False
         for parent, n, child in self.mods:
-            if parent._modules.get(n) is not child:
+            if (block if parent is None else parent)._modules.get(n) is not child:
                 return False
         for leaf, n, t, ptr in self.params:
             if leaf._parameters.get(n) is not t or (t is not None and t.data_ptr() != ptr):
@@ -222,13 +227,18 @@ class _CachedDesc:
 def _block_desc(block, attn_variant, gacc):
     """The block's fbb_block_desc, read afresh only when the block changed since the last call (raises like
     _fill_block_desc)."""
+    return _block_entry(block, attn_variant, gacc).desc
+
+
+def _block_entry(block, attn_variant, gacc):
     ent = _DESCS.get(block)
     if ent is None or not ent.valid(block, attn_variant, gacc):
         ent = _DESCS[block] = _CachedDesc(block, attn_variant, gacc)
-    return ent.desc
+    return ent
 
 
 _DESCS = weakref.WeakKeyDictionary()  # block module -> _CachedDesc (kept outside the module: nothing to copy or pickle)
+_STACK_SIZES = {}                    # see run_stack
 
 
 def run_stack(blocks, x, attn_variant, gacc):
@@ -238,26 +248,34 @@ def run_stack(blocks, x, attn_variant, gacc):
     n = len(blocks)
     descs = (_lib.BlockDesc * n)()
     try:
-        for i, b in enumerate(blocks):
-            descs[i] = _block_desc(b, attn_variant, gacc)
+        ents = [_block_entry(b, attn_variant, gacc) for b in blocks]
     except (LookupError, AttributeError):
         return False
+    for i, e in enumerate(ents):
+        descs[i] = e.desc
     if not (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() == 3 and x.shape[2] == descs[0].C):
         return False
     B, N, _ = x.shape
     if B == 0 or N == 0 or n == 0:
         return True
     lib = _lib.load()
-    with torch.cuda.device(x.device):
-        scratch = torch.empty(lib.fbb_stack_scratch_bytes(descs, n, B * N), device=x.device, dtype=torch.uint8)
-        need = lib.fbb_flash64_workspace_bytes(B, N, descs[0].heads)
-        ws = _workspace(x.device, need) if need > 0 else None
+    with _lib.on(x.device):
+        # scratch size, attention workspace size and launch count of this run of blocks at this shape: three C calls,
+        # remembered per (descriptors, shape, device) - they are a tenth of the host time of a ViT-S forward pass
+        key = (tuple(e.serial for e in ents), B, N, x.device.index)
+        sizes = _STACK_SIZES.get(key)
+        if sizes is None:
+            need = lib.fbb_flash64_workspace_bytes(B, N, descs[0].heads)
+            launches = lib.fbb_stack_launches(descs, n, B * N) + n * (lib.fbb_flash64_launches(B, N, descs[0].heads, int(need > 0)) - 1)
+            if len(_STACK_SIZES) >= 256:
+                _STACK_SIZES.clear()
+            sizes = _STACK_SIZES[key] = (lib.fbb_stack_scratch_bytes(descs, n, B * N), need, launches)
+        scratch = torch.empty(sizes[0], device=x.device, dtype=torch.uint8)
+        ws = _workspace(x.device, sizes[1]) if sizes[1] > 0 else None
         _lib.check(lib.fbb_stack_forward_f16(descs, n, x.data_ptr(), B, N, scratch.data_ptr(), scratch.numel(),
                                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
                                              _lib.stream_ptr(x.device)))
-    with _lib.on(x.device):  # (the attention launch count depends on the device's SM count)
-        flash = lib.fbb_flash64_launches(B, N, descs[0].heads, int(ws is not None))
-    _lib.launched(lib.fbb_stack_launches(descs, n, B * N) + n * (flash - 1))
+    _lib.launched(sizes[2])
     return True
 
 

@@ -188,3 +188,40 @@ def test_synthetic_generator_matches_the_oracles(oracle):
     a, b = synthetic.make_params("vitg14", seed=3, depth=1, num_register_tokens=4), oracle.make_params("vitg14", seed=3, depth=1, num_register_tokens=4)
     assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
     assert torch.equal(synthetic.make_image(2, 28, 42, seed=5), oracle.make_image(2, 28, 42, seed=5))
+
+
+def test_block_descriptor_cache_does_not_keep_the_block_alive(monkeypatch):
+    """The C runner's per-block descriptor cache is a weak-keyed table: an entry follows the block (same object while the
+    block is unchanged, re-read after a change) and goes away with it - neither the block nor its weights may be held by
+    the cache. (The descriptor fill itself needs CUDA tensors and is replaced here.)"""
+    import gc
+    import weakref
+    monkeypatch.setattr(fvit, "_fill_block_desc", lambda d, block, attn, gacc: None)
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.num_heads, self.qkv, self.proj = 2, nn.Linear(128, 384), nn.Linear(128, 128)
+
+    class Mlp(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.act, self.fc2 = nn.Linear(128, 512), nn.GELU(), nn.Linear(512, 128)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm1, self.norm2, self.attn, self.mlp = nn.LayerNorm(128), nn.LayerNorm(128), Attn(), Mlp()
+            self.ls1, self.ls2 = nn.Identity(), nn.Identity()
+
+    b = Block()
+    e = fvit._block_entry(b, "fh", False)
+    assert fvit._block_entry(b, "fh", False) is e and e.valid(b, "fh", False)
+    b.norm1.eps = 1e-3
+    assert not e.valid(b, "fh", False) and fvit._block_entry(b, "fh", False) is not e
+    b.mlp.fc2 = nn.Linear(512, 128)
+    assert not fvit._DESCS[b].valid(b, "fh", False)
+    rb, rw = weakref.ref(b), weakref.ref(b.attn.qkv.weight)
+    del b, e
+    gc.collect()
+    assert rb() is None and rw() is None
